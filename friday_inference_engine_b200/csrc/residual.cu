@@ -421,3 +421,184 @@ FR_EXPORT int residual_embed_rows(const int* tokens, const void* table, int tabl
     FR_CHECK_LAUNCH("embed_rows");
     return FR_OK;
 }
+
+// ------------------------------------------------------------------ a learned position table, token shift, norms around a sublayer
+namespace {
+
+// out[r] = table[token[r]] + positions[pos[r]], 32-bit
+template <typename TW>
+__global__ void embed_pos_kernel(const int* __restrict__ tokens, const int* __restrict__ row_pos, const TW* __restrict__ table,
+                                 const TW* __restrict__ positions, float* __restrict__ out, int width, int vocab, int max_pos) {
+    fr_pdl_wait();
+    fr_pdl_launch();
+    const int token = tokens[blockIdx.x], pos = row_pos[blockIdx.x];
+    float* o = out + (size_t)blockIdx.x * width;
+    const bool ok = token >= 0 && token < vocab && pos >= 0 && pos < max_pos;
+    const TW* t = table + (size_t)(ok ? token : 0) * width;
+    const TW* q = positions + (size_t)(ok ? pos : 0) * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = ok ? fr_load(t + i) + fr_load(q + i) : 0.f;
+}
+
+// h = x / sqrt(mean(x^2) + eps) * w per row; y = h + (h_before - h) * shift, where h_before is the same norm of the row
+// before in the sequence, or the sequence's kept row (state) for the first row of a step.  save: every row also leaves its
+// h in the state (steps of one row per sequence, where the block that reads the state is the one that writes it).
+template <typename TO>
+__global__ void __launch_bounds__(256)
+norm_shift_kernel(const float* __restrict__ x, FrVec w, FrVec shift, TO* __restrict__ y, float* __restrict__ state, long long state_stride,
+                  const int* __restrict__ row_seq, const int* __restrict__ seq_start, const int* __restrict__ seq_slots, int width,
+                  float eps, int save) {
+    __shared__ float partial[32];
+    fr_pdl_wait();
+    fr_pdl_launch();
+    const int row = blockIdx.x;
+    const int seq = row_seq[row];
+    if (seq < 0) return;
+    const bool first = row == seq_start[seq];
+    const float* xr = x + (size_t)row * width;
+    const float* xb = xr - width;
+    float* sp = state + (size_t)seq_slots[seq] * state_stride;
+    float ss = 0.f, sb = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = xr[i];
+        ss = fmaf(v, v, ss);
+        if (!first) {
+            const float u = xb[i];
+            sb = fmaf(u, u, sb);
+        }
+    }
+    ss = block_sum(ss, partial);
+    sb = block_sum(sb, partial);
+    const float inv = 1.0f / sqrtf(ss / (float)width + eps), invb = 1.0f / sqrtf(sb / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float wi = w.at(i);
+        const float h = xr[i] * inv * wi;
+        const float before = first ? sp[i] : xb[i] * invb * wi;
+        fr_store(y + (size_t)row * width + i, fmaf(before - h, shift.at(i), h));
+        if (save) sp[i] = h;
+    }
+}
+
+// the state keeps the norm of every sequence's last row of the step
+__global__ void __launch_bounds__(256)
+norm_keep_last_kernel(const float* __restrict__ x, FrVec w, float* __restrict__ state, long long state_stride,
+                      const int* __restrict__ seq_start, const int* __restrict__ seq_qlen, const int* __restrict__ seq_slots, int width,
+                      float eps) {
+    __shared__ float partial[32];
+    fr_pdl_wait();
+    fr_pdl_launch();
+    const int seq = blockIdx.x;
+    const int n = seq_qlen[seq];
+    if (n <= 0) return;
+    const float* xr = x + (size_t)(seq_start[seq] + n - 1) * width;
+    float* sp = state + (size_t)seq_slots[seq] * state_stride;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) ss = fmaf(xr[i], xr[i], ss);
+    ss = block_sum(ss, partial);
+    const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) sp[i] = xr[i] * inv * w.at(i);
+}
+
+// out = x + mult * y / sqrt(mean(y^2) + eps) * w; and, if asked for, the norm of `out` that the next sublayer reads:
+// next = out / sqrt(mean(out^2) + eps2) * w2 in the activation dtype
+template <typename TO>
+__global__ void __launch_bounds__(256)
+post_norm_add_kernel(const float* __restrict__ x, const float* __restrict__ y, FrVec w, float eps, float mult, float* __restrict__ out,
+                     FrVec w2, float eps2, TO* __restrict__ next, int width) {
+    __shared__ float partial[32];
+    fr_pdl_wait();
+    fr_pdl_launch();
+    const size_t base = (size_t)blockIdx.x * width;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) ss = fmaf(y[base + i], y[base + i], ss);
+    ss = block_sum(ss, partial);
+    const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+    float s2 = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float o = fmaf(mult, y[base + i] * inv * w.at(i), x[base + i]);
+        out[base + i] = o;
+        s2 = fmaf(o, o, s2);
+    }
+    if (next == nullptr) return;
+    s2 = block_sum(s2, partial);
+    const float inv2 = 1.0f / sqrtf(s2 / (float)width + eps2);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) fr_store(next + base + i, out[base + i] * inv2 * w2.at(i));
+}
+
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+// z > 0: softplus(p) z^2 + z / 2;  z <= 0: (1/2 + softplus(q)) (e^z - 1 - z) + z / 2;  (p, q) = pq[0], pq[1]
+template <typename T>
+__global__ void two_sided_act_kernel(T* __restrict__ z, long long n, FrVec pq) {
+    fr_pdl_wait();
+    fr_pdl_launch();
+    const float a = softplus_f(pq.at(0)), b = 0.5f + softplus_f(pq.at(1));
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const float v = fr_load(z + i);
+        fr_store(z + i, v > 0.f ? fmaf(a * v, v, 0.5f * v) : fmaf(b, expm1f(v) - v, 0.5f * v));
+    }
+}
+
+}  // namespace
+
+FR_EXPORT int residual_embed_pos(const int* tokens, const int* row_pos, const void* table, const void* positions, int table_dtype, float* out,
+                                 int n_rows, int width, int vocab, int max_pos, cudaStream_t stream) {
+    if (n_rows <= 0) return FR_OK;
+    if (table_dtype == FR_F32)
+        FR_CUDA(fr_launch(embed_pos_kernel<float>, dim3(n_rows), dim3(256), 0, stream, tokens, row_pos, (const float*)table,
+                          (const float*)positions, out, width, vocab, max_pos));
+    else if (table_dtype == FR_BF16)
+        FR_CUDA(fr_launch(embed_pos_kernel<bf16>, dim3(n_rows), dim3(256), 0, stream, tokens, row_pos, (const bf16*)table,
+                          (const bf16*)positions, out, width, vocab, max_pos));
+    else FR_REFUSE("embed_pos: unknown dtype %d", table_dtype);
+    FR_CHECK_LAUNCH("embed_pos");
+    return FR_OK;
+}
+
+// decode != 0: every sequence brings one row (the rows keep their norms themselves); otherwise a second kernel keeps the
+// norm of every sequence's last row once all rows have read what the state held.
+FR_EXPORT int residual_norm_shift(const float* x, const void* w, int w_dtype, const void* shift, int shift_dtype, void* y, int out_dtype,
+                                  float* state, long long state_stride, const int* row_seq, const int* seq_start, const int* seq_qlen,
+                                  const int* seq_slots, int n_rows, int n_seqs, int width, float eps, int decode, cudaStream_t stream) {
+    if (n_rows <= 0) return FR_OK;
+    if (state == nullptr || state_stride < width) FR_REFUSE("norm_shift: a state of at least the width per sequence");
+    const FrVec wv{w, w_dtype}, sv{shift, shift_dtype};
+    if (out_dtype == FR_F32)
+        FR_CUDA(fr_launch(norm_shift_kernel<float>, dim3(n_rows), dim3(256), 0, stream, x, wv, sv, (float*)y, state, state_stride, row_seq,
+                          seq_start, seq_slots, width, eps, decode ? 1 : 0));
+    else if (out_dtype == FR_BF16)
+        FR_CUDA(fr_launch(norm_shift_kernel<bf16>, dim3(n_rows), dim3(256), 0, stream, x, wv, sv, (bf16*)y, state, state_stride, row_seq,
+                          seq_start, seq_slots, width, eps, decode ? 1 : 0));
+    else FR_REFUSE("norm_shift: unknown dtype %d", out_dtype);
+    FR_CHECK_LAUNCH("norm_shift");
+    if (!decode) {
+        FR_CUDA(fr_launch(norm_keep_last_kernel, dim3(n_seqs), dim3(256), 0, stream, x, wv, state, state_stride, seq_start, seq_qlen,
+                          seq_slots, width, eps));
+        FR_CHECK_LAUNCH("norm_keep_last");
+    }
+    return FR_OK;
+}
+
+FR_EXPORT int residual_post_norm_add(const float* x, const float* y, const void* w, int w_dtype, float eps, float mult, float* out,
+                                     const void* w2, int w2_dtype, float eps2, void* next, int next_dtype, int n_rows, int width,
+                                     cudaStream_t stream) {
+    if (n_rows <= 0) return FR_OK;
+    const FrVec wv{w, w_dtype}, w2v{w2, w2_dtype};
+    if (next == nullptr || next_dtype == FR_F32)
+        FR_CUDA(fr_launch(post_norm_add_kernel<float>, dim3(n_rows), dim3(256), 0, stream, x, y, wv, eps, mult, out, w2v, eps2, (float*)next, width));
+    else if (next_dtype == FR_BF16)
+        FR_CUDA(fr_launch(post_norm_add_kernel<bf16>, dim3(n_rows), dim3(256), 0, stream, x, y, wv, eps, mult, out, w2v, eps2, (bf16*)next, width));
+    else FR_REFUSE("post_norm_add: unknown dtype %d", next_dtype);
+    FR_CHECK_LAUNCH("post_norm_add");
+    return FR_OK;
+}
+
+FR_EXPORT int residual_two_sided_act(void* z, long long n, int dtype, const void* pq, int pq_dtype, cudaStream_t stream) {
+    if (n <= 0) return FR_OK;
+    const FrVec v{pq, pq_dtype};
+    const unsigned blocks = (unsigned)((n + 1023) / 1024 < 4096 ? (n + 1023) / 1024 : 4096);
+    if (dtype == FR_F32) FR_CUDA(fr_launch(two_sided_act_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)z, n, v));
+    else if (dtype == FR_BF16) FR_CUDA(fr_launch(two_sided_act_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (bf16*)z, n, v));
+    else FR_REFUSE("two_sided_act: unknown dtype %d", dtype);
+    FR_CHECK_LAUNCH("two_sided_act");
+    return FR_OK;
+}

@@ -563,3 +563,101 @@ FR_EXPORT int routed_combine(const float* part, const int* ids, const float* wei
     FR_CHECK_LAUNCH("combine");
     return FR_OK;
 }
+
+// ------------------------------------------------------------------ a choice by biased sigmoid scores among groups of experts
+// Per row: s_e = sigmoid(z_e); the choice runs on c_e = s_e + bias_e (bias null: none).  The experts form `groups` equal
+// groups of neighbours; a group's score is the sum of its two largest c (of its one, if groups are single experts); only the
+// `keep` best groups' experts can be chosen (the others count as minus infinity).  The `top` largest c are chosen (the lower
+// index wins a tie, among groups as among experts); the weights are s_e * scale of the chosen, not renormalised.  fp32.
+namespace {
+
+__global__ void __launch_bounds__(128)
+route_scored_kernel(const float* __restrict__ logits, int ld, int rows, int experts, int top, FrVec bias, int groups, int keep,
+                    float scale, int* __restrict__ ids, float* __restrict__ weights, float* __restrict__ dense) {
+    __shared__ float s_all[4][32 * ROUTE_PER_LANE], c_all[4][32 * ROUTE_PER_LANE], g_all[4][32 * ROUTE_PER_LANE];
+    fr_pdl_wait();
+    fr_pdl_launch();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 4 + warp;
+    if (row >= rows) return;
+    float* s = s_all[warp];
+    float* c = c_all[warp];
+    float* gs = g_all[warp];
+    for (int e = lane; e < experts; e += 32) {
+        const float v = 1.0f / (1.0f + expf(-logits[(size_t)row * ld + e]));
+        s[e] = v;
+        c[e] = bias.p != nullptr ? v + bias.at(e) : v;
+        if (dense != nullptr) dense[(size_t)row * experts + e] = 0.f;
+    }
+    __syncwarp();
+    if (groups > 1) {
+        const int size = experts / groups;
+        for (int g = lane; g < groups; g += 32) {
+            float a = -INFINITY, b = -INFINITY;          // the two largest of the group
+            for (int i = 0; i < size; ++i) {
+                const float v = c[g * size + i];
+                if (v > a) { b = a; a = v; }
+                else if (v > b) b = v;
+            }
+            gs[g] = size > 1 ? a + b : a;
+        }
+        __syncwarp();
+        for (int g = lane; g < groups; g += 32) {
+            int better = 0;
+            for (int o = 0; o < groups; ++o) better += (gs[o] > gs[g] || (gs[o] == gs[g] && o < g)) ? 1 : 0;
+            if (better >= keep)
+                for (int i = 0; i < size; ++i) c[g * size + i] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    float z[ROUTE_PER_LANE];
+#pragma unroll
+    for (int i = 0; i < ROUTE_PER_LANE; ++i) z[i] = lane + 32 * i < experts ? c[lane + 32 * i] : -INFINITY;
+    int my_id = -1;
+    for (int t = 0; t < top; ++t) {
+        float best = -INFINITY;
+        int best_e = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < ROUTE_PER_LANE; ++i) {
+            const int e = lane + 32 * i;
+            if (e < experts && (z[i] > best || (z[i] == best && e < best_e))) {
+                best = z[i];
+                best_e = e;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (ob > best || (ob == best && oe < best_e)) {
+                best = ob;
+                best_e = oe;
+            }
+        }
+        if (best_e >= experts || best == -INFINITY) best_e = -1;          // nothing left that may be chosen
+        if (lane == (t & 31)) my_id = best_e;
+#pragma unroll
+        for (int i = 0; i < ROUTE_PER_LANE; ++i)
+            if (lane + 32 * i == best_e) z[i] = -INFINITY;
+    }
+    if (lane < top) {
+        const float w = my_id >= 0 ? s[my_id] * scale : 0.f;
+        ids[(size_t)row * top + lane] = my_id;
+        weights[(size_t)row * top + lane] = w;
+        if (dense != nullptr && my_id >= 0) dense[(size_t)row * experts + my_id] = w;
+    }
+}
+
+}  // namespace
+
+FR_EXPORT int routed_route_scored(const float* logits, int ld, int rows, int experts, int top, const void* bias, int bias_dtype, int groups,
+                                  int keep, float scale, int* ids, float* weights, float* dense, cudaStream_t stream) {
+    if (rows <= 0) return FR_OK;
+    if (experts < 1 || experts > 32 * ROUTE_PER_LANE) FR_REFUSE("route: %d experts (1 to %d)", experts, 32 * ROUTE_PER_LANE);
+    if (top < 1 || top > experts || top > 32) FR_REFUSE("route: top %d of %d experts (at most 32)", top, experts);
+    if (groups < 1 || experts % groups || keep < 1 || keep > groups) FR_REFUSE("route: %d experts in %d groups, %d kept", experts, groups, keep);
+    FR_CUDA(fr_launch(route_scored_kernel, dim3((rows + 3) / 4), dim3(128), 0, stream, logits, ld, rows, experts, top,
+                      FrVec{bias, bias_dtype}, groups, keep, scale, ids, weights, dense));
+    FR_CHECK_LAUNCH("route_scored");
+    return FR_OK;
+}

@@ -54,6 +54,11 @@ DecoderModel::DecoderModel(const ModelSpec& s, DType dtype) : spec(s) {
     for (const auto& inj : spec.injections) root_->declare(inj.weight, {spec.width, 2 * spec.width});
     for (const auto& sh : spec.shared) root_->declare(sh.first, sh.second);
     root_->declare(spec.embedding, {spec.vocab_size, spec.width});
+    if (!spec.position_table.empty()) {
+        if (!spec.residual_f32 || !spec.embed_norm.kind.empty() || spec.embed_scale != 1.0)
+            throw ConfigError("a learned position table is added to plain token rows of a 32-bit residual stream");
+        root_->declare(spec.position_table, {spec.max_positions, spec.width});
+    }
     if (!spec.head.empty()) root_->declare(spec.head, {spec.vocab_size, spec.width});
     if (!spec.head_bias.empty()) root_->declare(spec.head_bias, {spec.vocab_size});
 }
@@ -120,7 +125,8 @@ size_t load_params(const std::vector<StoredParam>& plan, WeightSource& source, O
         for (const auto& st : e.owner->stacked)
             if (st.first == e.decl.into) shape = &st.second;
         if (!shape) throw ConfigError("a parameter is stacked into '" + e.decl.into + "', which its part never declared");
-        auto mem = std::make_shared<DeviceBuffer>((size_t)(*shape)[0] * (*shape)[1] * dtype_size(s.dtype));
+        // zeroed: a stacked tensor may have rows that no parameter fills (the bias of a member that has none)
+        auto mem = std::make_shared<DeviceBuffer>((size_t)(*shape)[0] * (*shape)[1] * dtype_size(s.dtype), true);
         e.owner->set_tensor(e.decl.into, Tensor::make(mem->get(), s.dtype, *shape));
         e.owner->hold(mem);
         bytes += mem->bytes();
@@ -169,6 +175,7 @@ void DecoderModel::load(WeightSource& source, Ops& ops) {
     embedding = root_->tensor(spec.embedding);
     head = spec.head.empty() ? embedding : root_->tensor(spec.head);       // tied: one copy in memory
     if (!spec.head_bias.empty()) head_bias = root_->tensor(spec.head_bias);
+    if (!spec.position_table.empty()) position_table = root_->tensor(spec.position_table);
     injections.clear();
     for (const auto& inj : spec.injections) injections.push_back(root_->tensor(inj.weight));
     std::map<std::string, Tensor> shared;
@@ -185,7 +192,13 @@ DecoderModel::RunOut DecoderModel::run(Ops& ops, const StepContext& ctx, const s
                                        bool with_final_norm, Arena* layer_arenas[2]) {
     Arena* outer = ops.arena;
     Tensor x;
-    if (spec.residual_f32 && !embed_norm) {
+    PassValues values;                      // what layers leave for later layers lives in the caller's arena
+    values.arena = outer;
+    StepContext with_values = ctx;
+    with_values.values = &values;
+    if (position_table.defined()) {
+        x = ops.embed_pos_rows(ctx, embedding, position_table);
+    } else if (spec.residual_f32 && !embed_norm) {
         x = ops.embed_rows(ctx.tokens, ctx.rows, embedding, (float)spec.embed_scale);      // no rounding between table and stream
     } else {
         x = ops.embedding(ctx.tokens, ctx.rows, embedding);
@@ -223,7 +236,7 @@ DecoderModel::RunOut DecoderModel::run(Ops& ops, const StepContext& ctx, const s
         if (i + 1 < n) then = layers[spec.program[i + 1].layer]->first_norm();
         else if (with_final_norm) then = final_norm.get();
         static const CacheView none;
-        PartOut o = block->forward(ops, x, has_normed ? &normed : nullptr, ctx, call.cache >= 0 ? views[i] : none, then);
+        PartOut o = block->forward(ops, x, has_normed ? &normed : nullptr, with_values, call.cache >= 0 ? views[i] : none, then);
         x = o.x;
         if (dumping) dump_stream(ops, x, pass_no, i);
         has_normed = o.has_normed && then != nullptr;

@@ -35,7 +35,7 @@ public:
     std::unique_ptr<Norm> final_norm, embed_norm;
     std::vector<Tensor> injections;               // the matrices of ModelSpec::injections
     std::map<int, int> owners;                     // cache entry -> program entry that writes it
-    Tensor embedding, head, head_bias;
+    Tensor embedding, head, head_bias, position_table;
 
     // Every tensor the model needs, by full name (a layer that the run order names twice has its tensors once).
     std::vector<Part::Named> named_params();

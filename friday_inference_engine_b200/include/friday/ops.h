@@ -128,6 +128,19 @@ public:
     Tensor layernorm_to(const Tensor& x, const Tensor& weight, const Tensor* bias, float eps, DType out_dtype);
     // table[token] * scale as 32-bit rows: the start of a 32-bit residual stream, without a rounding in between
     Tensor embed_rows(const int* tokens, int64_t n, const Tensor& table, float scale);
+    // table[token] + positions[row_pos] as 32-bit rows: a learned position table beside the token table
+    Tensor embed_pos_rows(const StepContext& ctx, const Tensor& table, const Tensor& positions);
+    // y = h + (h_before - h) * shift with h = x / sqrt(mean(x^2) + eps) * weight (x: the 32-bit stream) and h_before the h of
+    // the row before in the sequence; the h before a step's first row comes from the state (`view`: a state of at least
+    // the width per sequence), which then keeps the h of the step's last row
+    Tensor norm_shift(const Tensor& x, const Tensor& weight, float eps, const Tensor& shift, const CacheView& view, const StepContext& ctx,
+                      DType out_dtype);
+    // x + mult * y / sqrt(mean(y^2) + eps) * weight (x, y 32-bit); with next_weight also the norm of that sum in `next_dtype`
+    // (what the sublayer after it reads), returned through `next`
+    Tensor post_norm_add(const Tensor& x, const Tensor& y, const Tensor& weight, float eps, float mult, const Tensor* next_weight = nullptr,
+                         float next_eps = 0.f, DType next_dtype = DType::F32, Tensor* next = nullptr);
+    // in place: z > 0: softplus(p) z^2 + z / 2; z <= 0: (1/2 + softplus(q)) (e^z - 1 - z) + z / 2; pq = (p, q)
+    void two_sided_act(Tensor& z, const Tensor& pq);
     // keys [n_kv_heads][head_dim] at column k_off and values [n_kv_heads][v_head_dim] at column v_off of every row of
     // `src` go to the cache rows of (row_seq, row_pos)
     void kv_store(const Tensor& src, int64_t k_off, int64_t v_off, const CacheView& view, const StepContext& ctx);
@@ -203,6 +216,9 @@ public:
         Tensor ids, weights, dense;     // [rows, top] int32, [rows, top] fp32, [rows, experts] fp32 (if asked for)
     };
     Routing route(const Tensor& logits, int top, bool softmax_all, bool with_dense);
+    // scores sigmoid(logit); the choice runs on score + bias (null: none) among the experts of the `keep` best of `groups`
+    // equal groups of neighbours (a group counts as the sum of its two largest); weights = score * scale of the chosen
+    Routing route_scored(const Tensor& logits, int top, const Tensor* bias, int groups, int keep, float scale, bool with_dense);
     void scale_by_route(Tensor& act, const Tensor& dense, int experts, int inner);
     Tensor expert_gate_up(const Tensor& h, const Routing& r, const Tensor& w_gate_up, int top, int inner);
     Tensor expert_down_combine(const Tensor& act, const Routing& r, const Tensor& w_down, const Tensor& residual, int top, int inner);
@@ -235,6 +251,23 @@ public:
     // (view.keep_first) and a multiplier of the result run on the CUDA-core kernel.
     void attention(const Tensor& q, int64_t q_stride, Tensor& out, const CacheView& view, const StepContext& ctx,
                    int n_heads, int n_kv_heads, int head_dim, int window, float scale, float out_scale = 1.0f);
+
+    // ---- attention whose heads' scores are mixed before the softmax (csrc/attention_talk.cu)
+    struct TalkSpec {
+        int heads = 0, kv_heads = 0, dim = 0, vdim = 0, window = 0;
+        float scale = 1.f;
+        const float* slopes = nullptr;  // device [heads]: slope_h * (i - j) is taken off head h's score; null: none
+        const Tensor* talk = nullptr;   // [heads, heads]: score_h <- sum_g talk[h][g] score_g; null: none
+        int64_t q_off = 0, k_off = 0, v_off = 0, gate_off = -1;     // columns of the stacked projection; gate_off < 0: no gate
+    };
+    // Keys and values of the step's rows go to the cache; blend (null: none) [rows, kv_heads * vdim] and lambda (one number):
+    // v <- (1 - lambda) v + lambda blend first, and the blended values are what is kept; keep (null: none) receives the
+    // values as stored
+    void talk_store(Tensor& proj, const TalkSpec& spec, const CacheView& view, const StepContext& ctx, const Tensor* blend,
+                    const Tensor* lambda, Tensor* keep);
+    // -> [rows, heads * vdim] in proj's dtype: softmax over the window of the mixed scores, times the values, times
+    // sigmoid(gate) element by element if the projection has gate columns
+    Tensor talk_attention(const Tensor& proj, const TalkSpec& spec, const CacheView& view, const StepContext& ctx);
 
     // ---- sampling: one id per row of logits [rows, vocab] fp32
     void sample(const Tensor& logits, const float* temperature, const int* streams, const int* steps,

@@ -18,6 +18,9 @@
 //                sequence, or nothing;  forward(ops, h, residual, ctx, view, then) ->
 //                residual + mix(h).
 //   FeedForward  forward(ops, h, residual, ctx, then) -> residual + f(h).
+//                A block that puts a norm between a sublayer and the sum hands the sublayer an undefined `residual`:
+//                the part then returns its own result alone, as 32-bit rows (the parts that blocks of that kind are
+//                built from do so: gqa_attention, dense, routed_experts).
 //   Block        cache_request() (its mixer's); forward(ops, x, normed, ctx, view, then).
 //   TokenInput   forward(ops, x, ctx): adds to the residual stream something that depends on the row's token
 //                (a per-layer token table, say), in place.
@@ -49,6 +52,7 @@
 namespace friday {
 
 class Ops;
+class Arena;
 struct Rows;
 struct StepContext;
 
@@ -83,6 +87,9 @@ struct ModelSpec {
     std::string architecture;
     int64_t vocab_size = 0, width = 0, max_positions = 0;
     std::string embedding;                      // tensor name of the token table [vocab, width]
+    // tensor name of a learned position table [max_positions, width] whose row of the token's position is added to the
+    // token's row (32-bit stream, not scaled); empty: none
+    std::string position_table;
     std::vector<PartSpec> layers;               // category "block"
     std::vector<LayerCall> program;
     PartSpec embed_norm;                        // kind empty: none; a norm applied to the token rows
@@ -140,6 +147,13 @@ struct CacheView {
     std::vector<CacheView> parts;
 };
 
+// Rows that one layer of a pass leaves for later layers of the same pass (the values of a first attention layer that
+// later ones blend their own with): kept by name, in memory that lives as long as the pass does.
+struct PassValues {
+    Arena* arena = nullptr;                // memory of the pass, not of a layer
+    std::map<std::string, Tensor> rows;
+};
+
 // ---- the geometry of one pass of the step function; parts read it, nothing writes it once it is built
 struct StepContext {
     int rows = 0, n_seqs = 0, max_q_len = 0, max_kv_len = 0;
@@ -152,6 +166,7 @@ struct StepContext {
     const int* seq_start = nullptr;        // first row of each sequence
     const int* seq_qlen = nullptr;
     const int* seq_pos0 = nullptr;         // position of each sequence's first row
+    PassValues* values = nullptr;          // what layers hand to later layers of this pass (set by the model's run loop)
 };
 
 struct BuildEnv {
@@ -224,6 +239,9 @@ public:
     using Part::Part;
     virtual Tensor forward(Ops& ops, const Tensor& x) = 0;
     virtual bool as_rmsnorm(Tensor* weight, float* eps) const { return false; }
+    // A norm of the form x / sqrt(mean(x^2) + eps) * weight answers with its parts whatever dtypes it reads and writes, so
+    // that a block may run it inside a kernel that does more (a token shift after it, a residual sum before it).
+    virtual bool rms_parts(Tensor* weight, float* eps) const { return false; }
 };
 
 class Position : public Part {

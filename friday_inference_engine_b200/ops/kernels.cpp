@@ -104,7 +104,9 @@ FAMILY(Residual, residual, "residual", resolve(h, fam, "residual_norm_cast", t.n
        resolve(h, fam, "residual_concat_cast", t.concat_cast); resolve(h, fam, "residual_add_scaled", t.add_scaled);
        resolve(h, fam, "residual_kv_store", t.kv_store); resolve(h, fam, "residual_token_input", t.token_input);
        resolve(h, fam, "residual_gelu_table", t.gelu_table); resolve(h, fam, "residual_rms_add", t.rms_add);
-       resolve(h, fam, "residual_layernorm_cast", t.layernorm_cast); resolve(h, fam, "residual_embed_rows", t.embed_rows);)
+       resolve(h, fam, "residual_layernorm_cast", t.layernorm_cast); resolve(h, fam, "residual_embed_rows", t.embed_rows);
+       resolve(h, fam, "residual_embed_pos", t.embed_pos); resolve(h, fam, "residual_norm_shift", t.norm_shift);
+       resolve(h, fam, "residual_post_norm_add", t.post_norm_add); resolve(h, fam, "residual_two_sided_act", t.two_sided_act);)
 FAMILY(Recurrence, recurrence, "recurrence", resolve(h, fam, "recurrence_shift_mix", t.shift_mix);
        resolve(h, fam, "recurrence_tanh_rows", t.tanh_rows); resolve(h, fam, "recurrence_scan", t.scan);
        resolve(h, fam, "recurrence_scan_plan", t.scan_plan);
@@ -113,7 +115,11 @@ FAMILY(Routed, routed, "routed", resolve(h, fam, "routed_route", t.route);
        resolve(h, fam, "routed_scale_by_route", t.scale_by_route); resolve(h, fam, "routed_gate_up", t.gate_up);
        resolve(h, fam, "routed_down_combine", t.down_combine);
        resolve(h, fam, "routed_down_scratch_floats", t.down_scratch_floats);
-       resolve(h, fam, "routed_sort_pairs", t.sort_pairs); resolve(h, fam, "routed_combine", t.combine);)
+       resolve(h, fam, "routed_sort_pairs", t.sort_pairs); resolve(h, fam, "routed_combine", t.combine);
+       resolve(h, fam, "routed_route_scored", t.route_scored);)
+FAMILY(AttentionTalk, attention_talk, "attention_talk", resolve(h, fam, "attention_talk_store", t.store);
+       resolve(h, fam, "attention_talk_stride", t.stride); resolve(h, fam, "attention_talk_scores", t.scores);
+       resolve(h, fam, "attention_talk_values", t.values);)
 FAMILY(Delta, delta, "delta", resolve(h, fam, "delta_conv_prepare", t.conv_prepare);
        resolve(h, fam, "delta_conv_state", t.conv_state); resolve(h, fam, "delta_scan", t.scan);)
 FAMILY(AttentionLatent, attention_latent, "attention_latent", resolve(h, fam, "attention_latent_rotate_pairs", t.rotate_pairs);

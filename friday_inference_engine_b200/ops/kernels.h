@@ -67,6 +67,12 @@ struct Residual {
     int (*rms_add)(float*, const float*, const void*, int, int, int, float, cudaStream_t);
     int (*layernorm_cast)(const void*, int, const void*, const void*, int, void*, int, int, int, float, cudaStream_t);
     int (*embed_rows)(const int*, const void*, int, float*, int, int, int, float, cudaStream_t);
+    int (*embed_pos)(const int*, const int*, const void*, const void*, int, float*, int, int, int, int, cudaStream_t);
+    int (*norm_shift)(const float*, const void*, int, const void*, int, void*, int, float*, long long, const int*, const int*, const int*,
+                      const int*, int, int, int, float, int, cudaStream_t);
+    int (*post_norm_add)(const float*, const float*, const void*, int, float, float, float*, const void*, int, float, void*, int, int, int,
+                         cudaStream_t);
+    int (*two_sided_act)(void*, long long, int, const void*, int, cudaStream_t);
 };
 struct Recurrence {
     last_error_fn last_error;
@@ -113,6 +119,17 @@ struct Routed {
     long long (*down_scratch_floats)(int, int, int, int, int);
     int (*sort_pairs)(const int*, int, int, int, int*, int*, int*, cudaStream_t);
     int (*combine)(const float*, const int*, const float*, const int*, const void*, void*, int, int, int, int, cudaStream_t);
+    int (*route_scored)(const float*, int, int, int, int, const void*, int, int, int, float, int*, float*, float*, cudaStream_t);
+};
+struct AttentionTalk {
+    last_error_fn last_error;
+    int (*store)(void*, int, int, int, int, int, int, const int*, const int*, void*, void*, const int*, int, int, int, int, const void*,
+                 const void*, int, void*, cudaStream_t);
+    long long (*stride)(int, int);
+    int (*scores)(const void*, int, const void*, const int*, int, int, const int*, const int*, int, int, int, int, int, int, float,
+                  const float*, const void*, int, float*, int, cudaStream_t);
+    int (*values)(const float*, const void*, const int*, int, int, const int*, const int*, int, int, int, int, int, int, const void*, int,
+                  void*, int, cudaStream_t);
 };
 struct AttentionMma {
     last_error_fn last_error;
@@ -145,6 +162,7 @@ const Recurrence& recurrence();
 const Routed& routed();
 const Delta& delta();
 const AttentionLatent& attention_latent();
+const AttentionTalk& attention_talk();
 
 // Called with a family's name when its library is missing; returns 0 when it has built it.
 typedef int (*builder_fn)(const char* family);

@@ -9,6 +9,8 @@
 #include "friday/ops.h"
 
 #include <stdlib.h>
+
+#include <algorithm>
 #include <string.h>
 
 #include "ops/kernels.h"
@@ -253,6 +255,109 @@ Tensor Ops::embed_rows(const int* tokens, int64_t n, const Tensor& table, float 
     call(launches_, k, k.embed_rows(tokens, table.data, code(table.dtype), (float*)o.data, (int)n, (int)table.cols(), (int)table.rows(),
                                     scale, stream_), "embed_rows");
     return o;
+}
+
+Tensor Ops::embed_pos_rows(const StepContext& ctx, const Tensor& table, const Tensor& positions) {
+    if (positions.cols() != table.cols() || positions.dtype != table.dtype || !positions.contiguous() || !table.contiguous())
+        throw KernelError("embed_pos_rows: a token table and a position table of one width and dtype");
+    Tensor o = alloc(DType::F32, ctx.rows, table.cols());
+    const auto& k = kernels::residual();
+    Timed t(*this, Other);
+    call(launches_, k, k.embed_pos(ctx.tokens, ctx.row_pos, table.data, positions.data, code(table.dtype), (float*)o.data, ctx.rows,
+                                   (int)table.cols(), (int)table.rows(), (int)positions.rows(), stream_), "embed_pos");
+    return o;
+}
+
+Tensor Ops::norm_shift(const Tensor& x, const Tensor& weight, float eps, const Tensor& shift, const CacheView& view, const StepContext& ctx,
+                       DType out_dtype) {
+    if (view.kind != CacheRequest::State || !view.state.defined()) throw KernelError("norm_shift needs a state view");
+    if (x.dtype != DType::F32 || !x.contiguous() || weight.numel() != x.cols() || shift.numel() != x.cols())
+        throw KernelError("norm_shift: a contiguous 32-bit stream, a weight and a shift of its width");
+    Tensor o = alloc(out_dtype, x.rows(), x.cols());
+    const long long stride = view.state.numel() / view.state.shape[0];
+    const auto& k = kernels::residual();
+    Timed t(*this, Other);
+    call(launches_, k, k.norm_shift((const float*)x.data, weight.data, code(weight.dtype), shift.data, code(shift.dtype), o.data,
+                                    code(out_dtype), (float*)view.state.data, stride, ctx.row_seq, ctx.seq_start, ctx.seq_qlen,
+                                    view.seq_slots, (int)x.rows(), ctx.n_seqs, (int)x.cols(), eps, ctx.decode ? 1 : 0, stream_),
+         "norm_shift");
+    if (!ctx.decode) ++launches_;
+    return o;
+}
+
+Tensor Ops::post_norm_add(const Tensor& x, const Tensor& y, const Tensor& weight, float eps, float mult, const Tensor* next_weight,
+                          float next_eps, DType next_dtype, Tensor* next) {
+    if (x.dtype != DType::F32 || y.dtype != DType::F32 || !x.contiguous() || !y.contiguous() || x.numel() != y.numel() ||
+        weight.numel() != x.cols() || (next_weight && (!next || next_weight->numel() != x.cols())))
+        throw KernelError("post_norm_add: a contiguous 32-bit stream, a 32-bit addend of its size and weights of its width");
+    Tensor o = alloc(DType::F32, x.rows(), x.cols());
+    if (next_weight) *next = alloc(next_dtype, x.rows(), x.cols());
+    const auto& k = kernels::residual();
+    Timed t(*this, Other);
+    call(launches_, k, k.post_norm_add((const float*)x.data, (const float*)y.data, weight.data, code(weight.dtype), eps, mult,
+                                       (float*)o.data, next_weight ? next_weight->data : nullptr, next_weight ? code(next_weight->dtype) : 0,
+                                       next_eps, next_weight ? next->data : nullptr, code(next_dtype), (int)x.rows(), (int)x.cols(), stream_),
+         "post_norm_add");
+    return o;
+}
+
+void Ops::two_sided_act(Tensor& z, const Tensor& pq) {
+    if (!z.contiguous() || pq.numel() != 2) throw KernelError("two_sided_act: contiguous rows and two numbers");
+    const auto& k = kernels::residual();
+    Timed t(*this, Other);
+    call(launches_, k, k.two_sided_act(z.data, (long long)z.numel(), code(z.dtype), pq.data, code(pq.dtype), stream_), "two_sided_act");
+}
+
+// ------------------------------------------------------------------ attention whose heads talk before the softmax
+void Ops::talk_store(Tensor& proj, const TalkSpec& s, const CacheView& view, const StepContext& ctx, const Tensor* blend,
+                     const Tensor* lambda, Tensor* keep) {
+    if (view.kind != CacheRequest::KV || !view.k_pool) throw KernelError("talk_store needs a view of keys and values");
+    if (view.dtype != proj.dtype) throw KernelError("talk_store: the cache's dtype differs from the rows'");
+    const int64_t vw = (int64_t)s.kv_heads * s.vdim;
+    if ((blend && (blend->dtype != proj.dtype || !blend->contiguous() || blend->rows() != proj.rows() || blend->cols() != vw || !lambda)) ||
+        (keep && (keep->dtype != proj.dtype || !keep->contiguous() || keep->rows() != proj.rows() || keep->cols() != vw)))
+        throw KernelError("talk_store: rows to blend with or to keep must be [rows, kv heads * value size] in the rows' dtype");
+    if (!view.write && !keep) return;
+    if (!view.write) throw KernelError("talk_store: a layer that leaves its values for others writes its own cache entry");
+    const auto& k = kernels::attention_talk();
+    Timed t(*this, Other);
+    call(launches_, k, k.store(proj.data, (int)proj.ld, (int)s.k_off, (int)s.v_off, s.kv_heads, s.dim, s.vdim, ctx.row_seq, ctx.row_pos,
+                               view.k_pool, view.v_pool, view.block_table, view.table_width, view.page_size, (int)proj.rows(),
+                               code(proj.dtype), blend ? blend->data : nullptr, lambda ? lambda->data : nullptr,
+                               lambda ? code(lambda->dtype) : 0, keep ? keep->data : nullptr, stream_), "talk_store");
+}
+
+Tensor Ops::talk_attention(const Tensor& proj, const TalkSpec& s, const CacheView& view, const StepContext& ctx) {
+    if (view.kind != CacheRequest::KV || !view.k_pool) throw KernelError("talk_attention needs a view of keys and values");
+    if (view.dtype != proj.dtype) throw KernelError("talk_attention: the cache's dtype differs from the rows'");
+    if (s.talk && (s.talk->numel() != (int64_t)s.heads * s.heads || !s.talk->contiguous()))
+        throw KernelError("talk_attention: the mixing matrix is [heads, heads]");
+    const auto& k = kernels::attention_talk();
+    const int64_t rows = proj.rows();
+    Tensor out = alloc(proj.dtype, rows, (int64_t)s.heads * s.vdim);
+    const long long stride = k.stride(s.window, ctx.max_kv_len);
+    // the mixed scores of all heads go through memory, [rows][heads][stride] floats: rows are taken in runs that keep it
+    // below a gigabyte
+    const int64_t per_row = (int64_t)s.heads * stride;
+    int64_t run = std::max<int64_t>(1, ((int64_t)1 << 28) / std::max<int64_t>(per_row, 1));
+    run = std::min(run, rows);
+    float* scores = scratch_floats(run * per_row);
+    const char* q = (const char*)proj.data + (size_t)s.q_off * dtype_size(proj.dtype);
+    const char* gate = s.gate_off >= 0 ? (const char*)proj.data + (size_t)s.gate_off * dtype_size(proj.dtype) : nullptr;
+    const size_t row_bytes = (size_t)proj.ld * dtype_size(proj.dtype);
+    for (int64_t r0 = 0; r0 < rows; r0 += run) {
+        const int n = (int)std::min(run, rows - r0);
+        Timed t(*this, Attention);
+        call(launches_, k, k.scores(q + r0 * row_bytes, (int)proj.ld, view.k_pool, view.block_table, view.table_width, view.page_size,
+                                    ctx.row_seq + r0, ctx.row_pos + r0, n, s.heads, s.kv_heads, s.dim, s.window, ctx.max_kv_len, s.scale,
+                                    s.slopes, s.talk ? s.talk->data : nullptr, s.talk ? code(s.talk->dtype) : 0, scores, code(proj.dtype),
+                                    stream_), "talk_scores");
+        call(launches_, k, k.values(scores, view.v_pool, view.block_table, view.table_width, view.page_size, ctx.row_seq + r0,
+                                    ctx.row_pos + r0, n, s.heads, s.kv_heads, s.vdim, s.window, ctx.max_kv_len,
+                                    gate ? gate + r0 * row_bytes : nullptr, (int)proj.ld,
+                                    (char*)out.data + (size_t)r0 * out.ld * dtype_size(out.dtype), code(proj.dtype), stream_), "talk_values");
+    }
+    return out;
 }
 
 void Ops::kv_store(const Tensor& src, int64_t k_off, int64_t v_off, const CacheView& view, const StepContext& ctx) {
@@ -531,6 +636,22 @@ Ops::Routing Ops::route(const Tensor& logits, int top, bool softmax_all, bool wi
     Timed t(*this, Other);
     call(launches_, k, k.route((const float*)logits.data, (int)logits.ld, (int)rows, (int)experts, top, softmax_all ? 1 : 0,
                                (int*)r.ids.data, (float*)r.weights.data, with_dense ? (float*)r.dense.data : nullptr, stream_), "route");
+    return r;
+}
+
+Ops::Routing Ops::route_scored(const Tensor& logits, int top, const Tensor* bias, int groups, int keep, float scale, bool with_dense) {
+    if (logits.dtype != DType::F32) throw KernelError("route: router logits are float32");
+    const int64_t rows = logits.rows(), experts = logits.cols();
+    if (bias && bias->numel() != experts) throw KernelError("route: the choice bias has a number per expert");
+    Routing r;
+    r.ids = Tensor::make(arena->alloc((size_t)rows * top * sizeof(int)), DType::I32, {rows, (int64_t)top});
+    r.weights = alloc(DType::F32, rows, top);
+    if (with_dense) r.dense = alloc(DType::F32, rows, experts);
+    const auto& k = kernels::routed();
+    Timed t(*this, Other);
+    call(launches_, k, k.route_scored((const float*)logits.data, (int)logits.ld, (int)rows, (int)experts, top, bias ? bias->data : nullptr,
+                                      bias ? code(bias->dtype) : 0, groups, keep, scale, (int*)r.ids.data, (float*)r.weights.data,
+                                      with_dense ? (float*)r.dense.data : nullptr, stream_), "route_scored");
     return r;
 }
 

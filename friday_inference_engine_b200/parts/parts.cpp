@@ -181,6 +181,12 @@ public:
         *eps = eps_;
         return true;
     }
+    bool rms_parts(Tensor* weight, float* eps) const override {
+        if (offset_ != 0.f) return false;
+        *weight = tensor(name_);
+        *eps = eps_;
+        return true;
+    }
 
 private:
     float eps_, offset_;
@@ -355,8 +361,23 @@ public:
         out_bias_ = s.params.get_bool("out_bias", false);
         position_ = adopt("", build<Position>("position", s.part("position"), e));
         const int64_t qd = (int64_t)nq_ * hd_, kvd = (int64_t)nkv_ * hd_, vvd = (int64_t)nkv_ * vd_, w = e.width;
-        declare_stacked("w_qkv", qd + kvd + vvd, w);
-        if (qkv_bias_) declare_stacked("b_qkv", qd + kvd + vvd, 1);      // a vector: one column, members under one another
+        // Heads that talk: "distance_slope_base" b > 0 takes 2^(-b (h + 1) / heads) * (i - j) off head h's score; "talk" names
+        // a tensor [heads, heads] that mixes the heads' scores before the softmax; "gate" names a projection [heads * v, width]
+        // whose sigmoid multiplies the heads' results element by element (it reads the mixer's input, like q, k and v);
+        // "value_mix": "first" leaves this layer's values for later layers of the pass under "value_mix_key", "blend" replaces
+        // v by (1 - lambda) v + lambda v_first before it is cached, lambda being the tensor "value_mix_weight".
+        slope_base_ = s.params.get_double("distance_slope_base", 0.0);
+        talk_name_ = s.params.get_string("talk", "");
+        gate_name_ = s.params.get_string("gate", "");
+        value_mix_ = s.params.get_string("value_mix", "");
+        value_key_ = s.params.get_string("value_mix_key", "values.first");
+        lambda_name_ = s.params.get_string("value_mix_weight", "vmix");
+        if (!value_mix_.empty() && value_mix_ != "first" && value_mix_ != "blend")
+            throw ConfigError("gqa_attention: 'value_mix' is \"first\", \"blend\" or absent");
+        talking_ = slope_base_ > 0.0 || !talk_name_.empty() || !gate_name_.empty() || !value_mix_.empty();
+        const int64_t gd = gate_name_.empty() ? 0 : (int64_t)nq_ * vd_;
+        declare_stacked("w_qkv", qd + kvd + vvd + gd, w);
+        if (qkv_bias_) declare_stacked("b_qkv", qd + kvd + vvd + gd, 1);      // a vector: one column, members under one another
         // tensor names: Hugging Face's unless the specification gives others ("names": {"q": ..., "k": ..., "v": ..., "o": ...})
         const Json* names = s.params.find("names");
         const char* roles[4] = {"q", "k", "v", "o"};
@@ -370,7 +391,7 @@ public:
                 bare = true;
             }
         }
-        const std::string wsuf = bare ? "" : ".weight", bsuf = ".bias";
+        const std::string wsuf = bare ? "" : ".weight", bsuf = s.params.get_string("bias_suffix", ".bias");
         const int64_t rows[3] = {qd, kvd, vvd}, first[3] = {0, qd, qd + kvd};
         for (int i = 0; i < 3; ++i) {
             declare(stem[i] + wsuf, {rows[i], w}).stack("w_qkv", first[i]);
@@ -380,8 +401,24 @@ public:
         o_bias_name_ = stem[3] + bsuf;
         declare(o_name_, {w, (int64_t)nq_ * vd_});
         if (out_bias_) declare(o_bias_name_, {w});
+        if (gd) declare(gate_name_, {gd, w}).stack("w_qkv", qd + kvd + vvd);      // its rows of the bias stay zero
+        if (!talk_name_.empty()) declare(talk_name_, {(int64_t)nq_, (int64_t)nq_});
+        if (value_mix_ == "blend") declare(lambda_name_, {});
+        if (talking_ && keep_first_ > 0) throw ConfigError("gqa_attention: kept first keys with talking heads are not built");
     }
     CacheRequest cache_request() const override { return CacheRequest::kv(nkv_, hd_, window_, vd_, keep_first_); }
+    void finalize(Ops& ops) override {
+        Mixer::finalize(ops);
+        if (slope_base_ <= 0.0) return;
+        std::vector<float> table((size_t)nq_);
+        for (int h = 0; h < nq_; ++h) table[(size_t)h] = (float)pow(2.0, -slope_base_ * (double)(h + 1) / (double)nq_);
+        auto mem = std::make_shared<DeviceBuffer>(table.size() * sizeof(float));
+        cuda_check(cudaMemcpyAsync(mem->get(), table.data(), table.size() * sizeof(float), cudaMemcpyHostToDevice, ops.stream()),
+                   "cudaMemcpyAsync");
+        cuda_check(cudaStreamSynchronize(ops.stream()), "cudaStreamSynchronize");
+        slopes_ = (const float*)mem->get();
+        hold(mem);
+    }
 
     PartOut forward(Ops& ops, const Rows& h, const Tensor& residual, const StepContext& ctx, const CacheView& view,
                     Norm* then) override {
@@ -396,6 +433,7 @@ public:
         const float* denominators = nullptr;
         int rotary_dim = 0;
         Tensor qkv;
+        if (talking_) return talking(ops, h, residual, ctx, view, w_qkv, b_qkv);
         if (position_->rotary(&denominators, &rotary_dim)) {
             if (vd_ != hd_) throw ConfigError("gqa_attention: a rotary encoding with values of another size than the keys is not built");
             qkv = ops.qkv_rope_write(h, w_qkv, b_qkv, ctx.row_seq, ctx.row_pos, denominators, rotary_dim, nq_, nkv_, hd_, &view);
@@ -421,11 +459,66 @@ public:
     }
 
 private:
+    // The talking form: one product for q, k, v and the gate; the position part may change q and k; keys and (blended) values
+    // go to the cache; scores of all heads, mixed, through the softmax and the values; gate; output product.
+    PartOut talking(Ops& ops, const Rows& h, const Tensor& residual, const StepContext& ctx, const CacheView& view, const Tensor& w_qkv,
+                    const Tensor* b_qkv) {
+        const float* denominators = nullptr;
+        int rotary_dim = 0;
+        if (position_->rotary(&denominators, &rotary_dim)) throw ConfigError("gqa_attention: talking heads with a rotary table in the product are not built");
+        Tensor qkv = ops.linear(h, w_qkv, b_qkv);
+        position_->apply(ops, qkv, ctx, nq_, nkv_, hd_);
+        Ops::TalkSpec sp;
+        sp.heads = nq_;
+        sp.kv_heads = nkv_;
+        sp.dim = hd_;
+        sp.vdim = vd_;
+        sp.window = window_;
+        sp.scale = scale_;
+        sp.slopes = slopes_;
+        sp.talk = talk_name_.empty() ? nullptr : &tensor(talk_name_);
+        sp.q_off = 0;
+        sp.k_off = (int64_t)nq_ * hd_;
+        sp.v_off = sp.k_off + (int64_t)nkv_ * hd_;
+        sp.gate_off = gate_name_.empty() ? -1 : sp.v_off + (int64_t)nkv_ * vd_;
+        const Tensor* blend = nullptr;
+        Tensor kept;
+        Tensor* keep = nullptr;
+        if (!value_mix_.empty()) {
+            if (!ctx.values) throw KernelError("gqa_attention: blending values needs the pass's shared rows");
+            if (value_mix_ == "first") {
+                if (ctx.values->rows.count(value_key_)) throw ConfigError("two layers leave their values under '" + value_key_ + "'");
+                kept = Tensor::make(ctx.values->arena->alloc((size_t)qkv.rows() * nkv_ * vd_ * dtype_size(qkv.dtype)), qkv.dtype,
+                                    {qkv.rows(), (int64_t)nkv_ * vd_});
+                keep = &kept;
+            } else {
+                auto it = ctx.values->rows.find(value_key_);
+                if (it == ctx.values->rows.end()) throw ConfigError("no earlier layer left values under '" + value_key_ + "' to blend with");
+                blend = &it->second;
+            }
+        }
+        ops.talk_store(qkv, sp, view, ctx, blend, blend ? &tensor(lambda_name_) : nullptr, keep);
+        if (keep) ctx.values->rows[value_key_] = kept;
+        Tensor mixed = ops.talk_attention(qkv, sp, view, ctx);
+        const Tensor& w_o = tensor(o_name_);
+        const Tensor* b_o = out_bias_ ? &tensor(o_bias_name_) : nullptr;
+        if (!residual.defined()) {                  // the block sums itself: the result alone, 32-bit
+            Tensor y = ops.linear(Rows(mixed), w_o, b_o, nullptr, (int)DType::F32);
+            if (out_scale != 1.0f) ops.scale_rows(y, out_scale);
+            return PartOut(y);
+        }
+        return PartOut(ops.linear_residual(Rows(mixed), w_o, b_o, residual, out_scale));
+    }
+
     int nq_, nkv_, hd_, vd_, window_, keep_first_;
     float scale_;
     bool qkv_bias_, out_bias_;
     Position* position_;
     std::string o_name_, o_bias_name_;
+    double slope_base_ = 0.0;
+    bool talking_ = false;
+    std::string talk_name_, gate_name_, value_mix_, value_key_, lambda_name_;
+    const float* slopes_ = nullptr;
 };
 
 // ------------------------------------------------------------------ gated feed-forward: x + Wd (silu(Wg h) * (Wu h))

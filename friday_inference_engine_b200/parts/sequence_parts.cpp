@@ -7,7 +7,8 @@
 //                                    w_t = exp(-exp(z_t))
 //   mixer "parallel"                 sum of scale_i * mixer_i(h) over members that read the same input, each with a cache
 //                                    entry part of its own
-//   feed_forward "routed_experts"    top-k of a biased router, weights by softmax over the chosen logits, gated experts
+//   feed_forward "routed_experts"    top-k of a biased router, weights by softmax over the chosen logits, gated experts; or
+//                                    sigmoid scores with a choice bias and groups of experts, and an expert for every row
 //   token_input "gated_token_table"  x += norm(proj(gelu_tanh(gate x) * table[token]))
 //
 // The states, the decays and everything that enters the recurrences besides the projections are fp32 (csrc/recurrence.cu);
@@ -227,9 +228,34 @@ public:
         softmax_all_ = s.params.get_bool("softmax_all", false);
         if (top_ > experts_) throw ConfigError(format("routed_experts: top %d of %d experts", top_, experts_));
         if (top_ > 32 || experts_ > 256) throw ConfigError("routed_experts: at most 256 experts and 32 choices");
+        // "score": "sigmoid" makes the scores sigmoid(logit): the choice runs on score + the tensor "choice_bias" (if named)
+        // among the experts of the "groups_keep" best of "groups" equal groups of neighbours (a group counts as the sum of its
+        // two largest), the weights are score * "weight_scale", not renormalised.  "router_bias": false leaves the logits'
+        // bias out.  "shared_inner" > 0 adds an expert of that inner size ("shared.") that every row uses.
+        const std::string score = s.params.get_string("score", "softmax");
+        if (score != "softmax" && score != "sigmoid") throw ConfigError("routed_experts: 'score' is \"softmax\" or \"sigmoid\"");
+        sigmoid_ = score == "sigmoid";
+        router_bias_ = s.params.get_bool("router_bias", true);
+        choice_bias_ = s.params.get_string("choice_bias", "");
+        groups_ = (int)s.params.get_int("groups", 1);
+        keep_ = (int)s.params.get_int("groups_keep", groups_);
+        weight_scale_ = (float)s.params.get_double("weight_scale", 1.0);
+        shared_inner_ = s.params.get_int("shared_inner", 0);
+        if (groups_ < 1 || experts_ % groups_ || keep_ < 1 || keep_ > groups_ || keep_ * (experts_ / groups_) < top_)
+            throw ConfigError(format("routed_experts: %d experts in %d groups of which %d are kept cannot give %d choices", experts_,
+                                     groups_, keep_, top_));
+        if (!sigmoid_ && (groups_ > 1 || !choice_bias_.empty() || weight_scale_ != 1.0f))
+            throw ConfigError("routed_experts: groups, a choice bias and a weight multiplier belong to sigmoid scores");
         const int64_t w = e.width;
         declare("router", {(int64_t)experts_, w});
-        declare("router.b", {(int64_t)experts_});
+        if (router_bias_) declare("router.b", {(int64_t)experts_});
+        if (!choice_bias_.empty()) declare(choice_bias_, {(int64_t)experts_});
+        if (shared_inner_ > 0) {
+            declare_stacked("w_shared", 2 * shared_inner_, w);
+            declare("shared.gate", {shared_inner_, w}).stack("w_shared", 0, 2);
+            declare("shared.up", {shared_inner_, w}).stack("w_shared", 1, 2);
+            declare("shared.down", {w, shared_inner_});
+        }
         declare_stacked("w_gate_up", (int64_t)experts_ * 2 * inner_, w);
         declare_stacked("w_down", w, (int64_t)experts_ * inner_);
         for (int x = 0; x < experts_; ++x) {
@@ -239,9 +265,20 @@ public:
             declare(p + "down", {w, (int64_t)inner_}).stack_columns("w_down", (int64_t)x * inner_);
         }
     }
-    PartOut forward(Ops& ops, const Rows& h, const Tensor& residual, const StepContext& ctx, Norm*) override {
+    PartOut forward(Ops& ops, const Rows& h, const Tensor& residual_in, const StepContext& ctx, Norm*) override {
         Tensor x = ops.materialize(h);
-        Tensor logits = ops.linear(Rows(x), tensor("router"), &tensor("router.b"), nullptr, (int)DType::F32);
+        Tensor logits = ops.linear(Rows(x), tensor("router"), router_bias_ ? &tensor("router.b") : nullptr, nullptr, (int)DType::F32);
+        // what the chosen experts' results are added to: the stream; with an expert that every row uses, its result on top
+        // of the stream; without a stream (a block that sums itself), that result alone or zeros, 32-bit
+        Tensor residual = residual_in;
+        if (shared_inner_ > 0) {
+            Tensor act = ops.linear_swiglu(Rows(x), tensor("w_shared"));
+            if (residual.defined()) residual = ops.linear_residual(Rows(act), tensor("shared.down"), nullptr, residual);
+            else residual = ops.linear(Rows(act), tensor("shared.down"), nullptr, nullptr, (int)DType::F32);
+        } else if (!residual.defined()) {
+            residual = ops.alloc(DType::F32, x.rows(), x.cols());
+            cuda_check(cudaMemsetAsync(residual.data, 0, residual.bytes(), ops.stream()), "cudaMemsetAsync");
+        }
         const bool tensor_cores = x.dtype == DType::BF16 && x.rows() > 32 && tensor("w_gate_up").dtype == DType::BF16 &&
                                   x.cols() % 8 == 0 && inner_ % 8 == 0;
         // Arithmetic of the dense form against the grouped one, in units of a product's multiply-adds: all experts for
@@ -258,7 +295,9 @@ public:
         const bool may_group = tensor_cores && !ctx.decode && ctx.rows == (int)x.rows() && ctx.n_seqs > 0;
         const bool grouped = may_group && (forced == "grouped" || (forced.empty() && grouped_work < dense_work));
         const bool dense = tensor_cores && !grouped && (forced == "dense" || (forced.empty() && experts_ <= 16 * top_));
-        Ops::Routing r = ops.route(logits, top_, softmax_all_, dense);
+        Ops::Routing r = sigmoid_ ? ops.route_scored(logits, top_, choice_bias_.empty() ? nullptr : &tensor(choice_bias_), groups_, keep_,
+                                                     weight_scale_, dense)
+                                  : ops.route(logits, top_, softmax_all_, dense);
         if (grouped) return PartOut(ops.experts_grouped(x, r, tensor("w_gate_up"), tensor("w_down"), residual, top_, inner_));
         if (dense) {
             Tensor act = ops.linear_swiglu(Rows(x), tensor("w_gate_up"));
@@ -272,6 +311,11 @@ public:
 private:
     int experts_, top_, inner_;
     bool softmax_all_;
+    bool sigmoid_ = false, router_bias_ = true;
+    std::string choice_bias_;
+    int groups_ = 1, keep_ = 1;
+    float weight_scale_ = 1.0f;
+    int64_t shared_inner_ = 0;
 };
 
 // ------------------------------------------------------------------ per-layer token input
