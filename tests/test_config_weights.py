@@ -92,7 +92,8 @@ def test_window_layers():
 def test_shipped_parts_are_registered():
     assert set(registered_parts("norm")) == {"rmsnorm", "layernorm"} and "gqa_attention" in registered_parts("mixer")
     assert set(registered_parts("position")) >= {"rotary_neox", "rotary_pairs", "none"}
-    assert set(registered_parts("feed_forward")) == {"swiglu", "routed_experts"} and registered_parts("block") == ["prenorm"]
+    assert set(registered_parts("feed_forward")) == {"swiglu", "routed_experts", "dense"}
+    assert set(registered_parts("block")) == {"prenorm", "sandwich"}
     assert set(registered_parts("mixer")) >= {"gated_linear_attention", "shift_decay_mix", "parallel", "gated_delta", "latent_attention"}
     assert registered_parts("token_input") == ["gated_token_table"]
     with pytest.raises(ConfigError):
