@@ -543,6 +543,53 @@ def sweeps(Engine, args):
     return 0
 
 
+def ditenex_config(width, layers=7, vocab=32768, window=1024, experts=8, top=2):
+    """A Ditenex configuration whose layers have sizes like a real model's of this width: heads of 128 key and 128 value
+    channels on a quarter as many key/value heads, a window of `window` tokens, every layer blending its values with the
+    first layer's; a dense feed-forward of three times the width in the even layers, `experts` experts of inner size
+    `width` in four groups of which two are kept, `top` chosen, and an expert of that size for every token, in the odd."""
+    heads = max(1, width // 128)
+    mixer = {"heads": heads, "kv_heads": max(1, width // 512), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+             "mask": {"size": window}, "v_mix": True}
+    dense = {"kind": "dense", "ff": 3 * width}
+    moe = {"kind": "moe", "expert": {"ff": width}, "shared": {"ff": width},
+           "router": {"experts": experts, "top": top, "scale": 1.5, "groups": {"count": 4, "keep": 2}}}
+    ls = [{"type": "attention", "mixer": mixer, "mlp": dense if i % 2 == 0 else moe} for i in range(layers)]
+    return {"architecture": "Ditenex", "vocab": vocab, "width": width, "max_positions": 4096, "residual_mult": 0.5,
+            "norm": {"eps": 1e-6}, "layers": ls}
+
+
+def ditenex_numbers(cfg, batch, context, prompt_len):
+    """What a decode step of `batch` sequences must read and what a prompt token costs (the chosen experts only; the
+    attention's share is that of a prompt of prompt_len tokens behind the window; the heads' mixing is not counted)."""
+    w, v = cfg["width"], cfg["vocab"]
+    weight_bytes = 2 * v * w
+    kv_bytes = 0
+    flops = 2 * v * w
+    for L in cfg["layers"]:
+        m = L["mixer"]
+        H, G, d, vd, win = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["mask"]["size"]
+        mat = (H * d + G * d + G * vd + H * vd) * w + w * H * vd
+        seen = sum(min(i + 1, win) for i in range(prompt_len)) / prompt_len
+        att = 2 * H * (d + vd) * seen
+        kv_bytes += batch * min(context, win) * G * (d + vd) * 2
+        weight_bytes += 2 * mat
+        flops += 2 * mat + att
+        mlp = L.get("mlp")
+        if not mlp:
+            continue
+        if mlp["kind"] == "dense":
+            weight_bytes += 2 * 2 * mlp["ff"] * w
+            flops += 2 * 2 * mlp["ff"] * w
+            continue
+        e, top, f = mlp["router"]["experts"], mlp["router"]["top"], mlp["expert"]["ff"]
+        sh = mlp["shared"]["ff"] if mlp.get("shared") else 0
+        distinct = e * (1.0 - (1.0 - top / e) ** batch)
+        weight_bytes += 2 * (e * w + (distinct * f + sh) * 3 * w)
+        flops += 2 * (e * w + (top * f + sh) * 3 * w)
+    return {"step_bytes": weight_bytes + kv_bytes, "flops_per_token": flops}
+
+
 def tikunex_config(width, layers=4, vocab=32768, window=1024, experts=8, top=2):
     """A Tikunex configuration whose layers have sizes like a real model's of this width: gated linear attention with
     keys of half and values of the full width; windowed attention (keys of 64, values of 128) beside shift-decay mixing
@@ -649,7 +696,7 @@ def tikunex_numbers(cfg, batch, context):
 
 
 def design_compare(Engine, args):
-    """Beletar and Tikunex beside the Qwen2.5 dense decoder at equal width and depth (random weights): one prompt and decode
+    """Ditenex, Beletar and Tikunex beside the Qwen2.5 dense decoder at equal width and depth (random weights): one prompt and decode
     steps, with the share of each kind of kernel in the prompt (event-bracketed).  One line of text per measurement.
     --designs picks among them."""
     pk = peaks()
@@ -657,6 +704,7 @@ def design_compare(Engine, args):
     for width in [int(v) for v in args.design_compare.split(",") if v]:
         layers = args.layers or 4
         designs = [
+            ("ditenex", ditenex_config(width, 2 * layers - 1)),
             ("beletar", beletar_config(width, layers)),
             ("tikunex", tikunex_config(width, layers)),
             ("qwen2", dict(QWEN25_7B, num_hidden_layers=2 * layers - 1, hidden_size=width, num_attention_heads=width // 128,
@@ -666,7 +714,10 @@ def design_compare(Engine, args):
             if name not in args.designs.split(","):
                 continue
             eng = Engine(config=cfg, seed=0, dtype="bfloat16", max_ctx=4096, max_batch=batch, max_tokens=batch * 4096 + 8192)
-            if name == "beletar":
+            if name == "ditenex":
+                nums = ditenex_numbers(cfg, batch, context + 64, prompt_len)
+                flops_tok, step_bytes = nums["flops_per_token"], nums["step_bytes"]
+            elif name == "beletar":
                 nums = beletar_numbers(cfg, batch, context + 64, prompt_len)
                 flops_tok, step_bytes = nums["flops_per_token"], nums["step_bytes"]
             elif name == "tikunex":
@@ -733,9 +784,9 @@ def main():
     ap.add_argument("--prefill-chunk", type=int, default=0, dest="prefill_chunk",
                     help="most tokens of a sequence per pass in the sweeps (0: the engine's own)")
     ap.add_argument("--design-compare", default="", dest="design_compare",
-                    help="widths, e.g. 1024,2048,4096: a Beletar and a Tikunex model with layers of that size beside the Qwen2.5 "
+                    help="widths, e.g. 1024,2048,4096: a Ditenex, a Beletar and a Tikunex model with layers of that size beside the Qwen2.5 "
                          "decoder of equal width (prompt, decode steps, kernel shares): lines of text")
-    ap.add_argument("--designs", default="beletar,tikunex,qwen2", help="which designs --design-compare runs")
+    ap.add_argument("--designs", default="ditenex,beletar,tikunex,qwen2", help="which designs --design-compare runs")
     ap.add_argument("--timeline", action="store_true",
                     help="print the kernels of one decode step as they run inside the captured graph (torch profiler)")
     args = ap.parse_args()

@@ -31,9 +31,8 @@ typedef __nv_bfloat16 bf16;
 
 namespace {
 
-constexpr int KT = 128;            // keys per block of the CUDA-core score kernel
-constexpr int DC = 32;             // channels staged at a time
-constexpr int HC = 4;              // heads whose weights the value kernel holds at a time
+constexpr int KS = 64;             // keys per block of the CUDA-core kernel
+constexpr int HC = 4;              // heads whose weighted values a thread sums at a time
 
 // ------------------------------------------------------------------ store
 template <typename T>
@@ -65,197 +64,239 @@ __global__ void talk_store_kernel(T* __restrict__ src, int ld, int k_off, int v_
     }
 }
 
-// ------------------------------------------------------------------ scores, CUDA cores
-struct ScoreArgs {
+// ------------------------------------------------------------------ a row's keys in splits, CUDA cores
+struct SplitArgs {
     const void* q;
     int q_ld;
     const void* k_pool;
-    const int* table;
-    int table_width, page;
-    const int* row_seq;
-    const int* row_pos;
-    int heads, kv_heads, dim, window, stride;
-    float scale;
-    const float* slopes;        // [heads] or null
-    FrVec talk;                 // [heads][heads] or null
-    float* out;                 // [rows][heads][stride]
-};
-
-template <typename T>
-__global__ void __launch_bounds__(KT) talk_scores_kernel(ScoreArgs p) {
-    extern __shared__ float sm[];
-    const int H = p.heads, G = p.kv_heads, dim = p.dim, per = H / G;
-    float* qs = sm;                         // [H][dim]
-    float* ss = qs + (size_t)H * dim;       // [H][KT]
-    float* kt = ss + (size_t)H * KT;        // [KT][DC + 1]
-    float* tk = kt + KT * (DC + 1);         // [H][H]
-    const int row = blockIdx.y, tid = threadIdx.x;
-    const int seq = p.row_seq[row];
-    fr_pdl_wait();
-    fr_pdl_launch();
-    if (seq < 0) return;
-    const int pos = p.row_pos[row];
-    const int j0 = max(0, pos - p.window + 1), n = pos - j0 + 1;
-    const int t0 = blockIdx.x * KT;
-    if (t0 >= n) return;
-    const T* q = (const T*)p.q + (size_t)row * p.q_ld;
-    for (int i = tid; i < H * dim; i += KT) qs[i] = fr_load(q + i);
-    if (p.talk.p != nullptr)
-        for (int i = tid; i < H * H; i += KT) tk[i] = p.talk.at(i);
-    const int* tab = p.table + (size_t)seq * p.table_width;
-    const T* kp = (const T*)p.k_pool;
-    const int t = t0 + tid;
-    const float dist = (float)(pos - (j0 + t));
-    for (int c = 0; c < G; ++c) {
-        for (int hc = 0; hc < per; hc += 8) {
-            float acc[8];
-#pragma unroll
-            for (int a = 0; a < 8; ++a) acc[a] = 0.f;
-            for (int d0 = 0; d0 < dim; d0 += DC) {
-                __syncthreads();
-                for (int idx = tid; idx < KT * DC; idx += KT) {
-                    const int kk = idx / DC, d = idx % DC;
-                    float v = 0.f;
-                    if (t0 + kk < n && d0 + d < dim) {
-                        const int j = j0 + t0 + kk;
-                        const size_t at = (size_t)tab[j / p.page] * p.page + j % p.page;
-                        v = fr_load(kp + (at * G + c) * dim + d0 + d);
-                    }
-                    kt[kk * (DC + 1) + d] = v;
-                }
-                __syncthreads();
-                const int dn = min(DC, dim - d0);
-#pragma unroll
-                for (int a = 0; a < 8; ++a) {
-                    if (hc + a < per) {
-                        const float* qh = qs + (size_t)(c * per + hc + a) * dim + d0;
-                        float s = acc[a];
-                        for (int d = 0; d < dn; ++d) s = fmaf(qh[d], kt[tid * (DC + 1) + d], s);
-                        acc[a] = s;
-                    }
-                }
-            }
-#pragma unroll
-            for (int a = 0; a < 8; ++a) {
-                if (hc + a < per) {
-                    const int h = c * per + hc + a;
-                    float s = acc[a] * p.scale;
-                    if (p.slopes != nullptr) s -= p.slopes[h] * dist;
-                    ss[h * KT + tid] = s;
-                }
-            }
-        }
-    }
-    __syncthreads();
-    if (t >= n) return;
-    float* o = p.out + (size_t)row * H * p.stride + t;
-    for (int h = 0; h < H; ++h) {
-        float s;
-        if (p.talk.p != nullptr) {
-            s = 0.f;
-            for (int g = 0; g < H; ++g) s = fmaf(tk[h * H + g], ss[g * KT + tid], s);
-        } else {
-            s = ss[h * KT + tid];
-        }
-        o[(size_t)h * p.stride] = s;
-    }
-}
-
-// ------------------------------------------------------------------ softmax and values, CUDA cores
-struct ValueArgs {
-    const float* scores;        // [rows][heads][stride]
     const void* v_pool;
     const int* table;
     int table_width, page;
     const int* row_seq;
     const int* row_pos;
-    int heads, kv_heads, vdim, window, stride;
-    const void* gate;           // [rows][gate_ld], head h's gates at h * vdim; or null
-    int gate_ld;
-    void* out;                  // [rows][heads * vdim]
+    int heads, kv_heads, dim, vdim, window, splits;
+    float scale;
+    const float* slopes;        // [heads] or null
+    FrVec talk;                 // [heads][heads] or null
+    float* part;                // [rows][splits][heads][vdim + 2]: weighted values (unnormalised), maximum, sum
 };
 
-constexpr int VK = 256;            // keys whose weights are held at a time
-
+template <typename T, int VEC>
+struct Chunk;                   // VEC neighbouring channels of a key as floats
 template <typename T>
-__global__ void __launch_bounds__(128) talk_values_kernel(ValueArgs p) {
-    __shared__ float w[HC][VK];
-    __shared__ float top[HC], inv[HC];
-    const int H = p.heads, G = p.kv_heads, vd = p.vdim, per = H / G;
-    const int row = blockIdx.x, c = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+struct Chunk<T, 1> {
+    static __device__ __forceinline__ void load(const T* p, float (&f)[1]) { f[0] = fr_load(p); }
+};
+template <>
+struct Chunk<float, 4> {
+    static __device__ __forceinline__ void load(const float* p, float (&f)[4]) {
+        const float4 v = *(const float4*)p;
+        f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+    }
+};
+template <>
+struct Chunk<bf16, 8> {
+    static __device__ __forceinline__ void load(const bf16* p, float (&f)[8]) {
+        const uint4 v = *(const uint4*)p;
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            f[2 * i] = __uint_as_float(w[i] << 16);
+            f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+};
+
+// A block owns KS consecutive keys of one row's window and every head.  Four neighbouring lanes share a key: each takes
+// every fourth chunk of VEC channels, two shuffles sum the parts.  The raw scores of all heads are mixed in shared memory,
+// each head's maximum and sum over the block's keys are found by a warp, and the weighted values of the block's keys are
+// summed with a thread per value channel.  What the block leaves is merged with the other blocks' by `talk_merge_kernel`.
+template <typename T, int VEC>
+__global__ void __launch_bounds__(128) talk_split_kernel(SplitArgs p) {
+    extern __shared__ __align__(16) float sm[];
+    const int H = p.heads, G = p.kv_heads, dim = p.dim, vd = p.vdim, per = H / G;
+    int* koff = (int*)sm;                               // [KS] cache row of each key
+    float* ms = sm + KS;                                // [H][KS] mixed scores, then weights
+    float* ss = ms + (size_t)H * KS;                    // [H][KS] raw scores
+    float* qs = ss + (size_t)H * KS;                    // [H][dim]
+    float* tk = qs + (size_t)H * dim;                   // [H][H]
+    float* stat = tk + (size_t)H * H;                   // [H][2]
+    const int row = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int seq = p.row_seq[row];
     fr_pdl_wait();
     fr_pdl_launch();
     if (seq < 0) return;
     const int pos = p.row_pos[row];
     const int j0 = max(0, pos - p.window + 1), n = pos - j0 + 1;
+    const int t0 = blockIdx.x * KS;
+    if (t0 >= n) return;
+    const int kn = min(KS, n - t0);
+    const T* q = (const T*)p.q + (size_t)row * p.q_ld;
+    for (int i = tid; i < H * dim; i += 128) qs[i] = fr_load(q + i);
+    if (p.talk.p != nullptr)
+        for (int i = tid; i < H * H; i += 128) tk[i] = p.talk.at(i);
     const int* tab = p.table + (size_t)seq * p.table_width;
-    const T* vp = (const T*)p.v_pool;
-    for (int hc = 0; hc < per; hc += HC) {
-        const int nh = min(HC, per - hc);
-        __syncthreads();
-        if (warp < nh) {                    // a warp per head: maximum, then the sum of the exponentials
-            const float* s = p.scores + ((size_t)row * H + c * per + hc + warp) * p.stride;
-            float m = -INFINITY;
-            for (int t = lane; t < n; t += 32) m = fmaxf(m, s[t]);
-            m = fr_warp_max(m);
-            float sum = 0.f;
-            for (int t = lane; t < n; t += 32) sum += expf(s[t] - m);
-            sum = fr_warp_sum(sum);
-            if (lane == 0) {
-                top[warp] = m;
-                inv[warp] = 1.0f / sum;
+    for (int t = tid; t < KS; t += 128) {
+        const int j = j0 + t0 + min(t, kn - 1);
+        koff[t] = tab[j / p.page] * p.page + j % p.page;
+    }
+    __syncthreads();
+    const T* kp = (const T*)p.k_pool;
+    const int c = tid & 3, nchunks = dim / VEC;
+    for (int pass = 0; pass < KS / 32; ++pass) {
+        const int t = pass * 32 + (tid >> 2);
+        const float dist = (float)(pos - (j0 + t0 + t));
+        const T* krow = kp + (size_t)koff[t] * G * dim;
+        for (int g = 0; g < G; ++g) {
+            for (int hc = 0; hc < per; hc += 8) {
+                float acc[8];
+#pragma unroll
+                for (int a = 0; a < 8; ++a) acc[a] = 0.f;
+                for (int ci = c; ci < nchunks; ci += 4) {
+                    float kf[VEC];
+                    Chunk<T, VEC>::load(krow + (size_t)g * dim + ci * VEC, kf);
+#pragma unroll
+                    for (int a = 0; a < 8; ++a) {
+                        if (hc + a < per) {
+                            const float* qh = qs + (size_t)(g * per + hc + a) * dim + ci * VEC;
+                            float s = acc[a];
+                            if (VEC % 4 == 0) {                 // 16-byte pieces: dim is a multiple of VEC
+#pragma unroll
+                                for (int e = 0; e < VEC / 4; ++e) {
+                                    const float4 qv = *(const float4*)(qh + 4 * e);
+                                    s = fmaf(qv.x, kf[4 * e], fmaf(qv.y, kf[4 * e + 1], fmaf(qv.z, kf[4 * e + 2], fmaf(qv.w, kf[4 * e + 3], s))));
+                                }
+                            } else {
+#pragma unroll
+                                for (int e = 0; e < VEC; ++e) s = fmaf(qh[e], kf[e], s);
+                            }
+                            acc[a] = s;
+                        }
+                    }
+                }
+#pragma unroll
+                for (int a = 0; a < 8; ++a) {
+                    if (hc + a < per) {
+                        float s = acc[a];
+                        s += __shfl_xor_sync(0xffffffffu, s, 1);
+                        s += __shfl_xor_sync(0xffffffffu, s, 2);
+                        if (c == 0) {
+                            const int h = g * per + hc + a;
+                            s *= p.scale;
+                            if (p.slopes != nullptr) s -= p.slopes[h] * dist;
+                            ss[h * KS + t] = s;
+                        }
+                    }
+                }
             }
         }
-        for (int d0 = 0; d0 < vd; d0 += 256) {
-            float acc[HC][2];
+    }
+    __syncthreads();
+    for (int idx = tid; idx < H * KS; idx += 128) {
+        const int h = idx / KS, t = idx - h * KS;
+        float s;
+        if (p.talk.p != nullptr) {
+            s = 0.f;
+            for (int g = 0; g < H; ++g) s = fmaf(tk[h * H + g], ss[g * KS + t], s);
+        } else {
+            s = ss[idx];
+        }
+        ms[idx] = t < kn ? s : -INFINITY;
+    }
+    __syncthreads();
+    for (int h = warp; h < H; h += 4) {
+        float* s = ms + (size_t)h * KS;
+        float m = -INFINITY;
+        for (int t = lane; t < KS; t += 32) m = fmaxf(m, s[t]);
+        m = fr_warp_max(m);
+        float sum = 0.f;
+        for (int t = lane; t < KS; t += 32) {
+            const float w = expf(s[t] - m);            // keys beyond the row's last: exp(-inf) = 0
+            s[t] = w;
+            sum += w;
+        }
+        sum = fr_warp_sum(sum);
+        if (lane == 0) {
+            stat[2 * h] = m;
+            stat[2 * h + 1] = sum;
+        }
+    }
+    __syncthreads();
+    const T* vp = (const T*)p.v_pool;
+    float* part = p.part + ((size_t)row * p.splits + blockIdx.x) * H * (vd + 2);
+    const int kn4 = (kn + 3) & ~3;                      // the weights past kn are zero, their rows the last key's
+    for (int d = tid; d < vd; d += 128) {
+        for (int g = 0; g < G; ++g) {
+            for (int hc = 0; hc < per; hc += HC) {
+                float acc[HC];
 #pragma unroll
-            for (int a = 0; a < HC; ++a) acc[a][0] = acc[a][1] = 0.f;
-            const int da = d0 + tid, db = d0 + 128 + tid;
-            for (int k0 = 0; k0 < n; k0 += VK) {
-                const int kn = min(VK, n - k0);
-                __syncthreads();
-                if (warp < nh) {
-                    const float* s = p.scores + ((size_t)row * H + c * per + hc + warp) * p.stride + k0;
-                    const float m = top[warp], r = inv[warp];
-                    for (int t = lane; t < kn; t += 32) w[warp][t] = expf(s[t] - m) * r;
-                }
-                __syncthreads();
-                for (int t = 0; t < kn; ++t) {
-                    const int j = j0 + k0 + t;
-                    const size_t at = (size_t)tab[j / p.page] * p.page + j % p.page;
-                    const T* vr = vp + (at * G + c) * vd;
-                    const float va = da < vd ? fr_load(vr + da) : 0.f;
-                    const float vb = db < vd ? fr_load(vr + db) : 0.f;
+                for (int a = 0; a < HC; ++a) acc[a] = 0.f;
+                for (int t = 0; t < kn4; t += 4) {
+                    const int4 at = *(const int4*)(koff + t);
+                    const float v0 = fr_load(vp + ((size_t)at.x * G + g) * vd + d);
+                    const float v1 = fr_load(vp + ((size_t)at.y * G + g) * vd + d);
+                    const float v2 = fr_load(vp + ((size_t)at.z * G + g) * vd + d);
+                    const float v3 = fr_load(vp + ((size_t)at.w * G + g) * vd + d);
 #pragma unroll
                     for (int a = 0; a < HC; ++a) {
-                        if (a < nh) {
-                            const float x = w[a][t];
-                            acc[a][0] = fmaf(x, va, acc[a][0]);
-                            acc[a][1] = fmaf(x, vb, acc[a][1]);
+                        if (hc + a < per) {
+                            const float4 w = *(const float4*)(ms + (size_t)(g * per + hc + a) * KS + t);
+                            acc[a] = fmaf(w.x, v0, fmaf(w.y, v1, fmaf(w.z, v2, fmaf(w.w, v3, acc[a]))));
                         }
                     }
                 }
-            }
 #pragma unroll
-            for (int a = 0; a < HC; ++a) {
-                if (a < nh) {
-                    const int h = c * per + hc + a;
-#pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        const int d = u == 0 ? da : db;
-                        if (d < vd) {
-                            float o = acc[a][u];
-                            if (p.gate != nullptr) {
-                                const float g = fr_load((const T*)p.gate + (size_t)row * p.gate_ld + (size_t)h * vd + d);
-                                o *= 1.0f / (1.0f + expf(-g));
-                            }
-                            fr_store((T*)p.out + (size_t)row * H * vd + (size_t)h * vd + d, o);
-                        }
-                    }
-                }
+                for (int a = 0; a < HC; ++a)
+                    if (hc + a < per) part[(size_t)(g * per + hc + a) * (vd + 2) + d] = acc[a];
             }
         }
+    }
+    for (int h = tid; h < H; h += 128) {
+        part[(size_t)h * (vd + 2) + vd] = stat[2 * h];
+        part[(size_t)h * (vd + 2) + vd + 1] = stat[2 * h + 1];
+    }
+}
+
+struct MergeTalkArgs {
+    const float* part;          // [rows][splits][heads][vdim + 2]
+    const int* row_seq;
+    const int* row_pos;
+    int heads, vdim, window, splits;
+    const void* gate;           // [rows][gate_ld], head h's gates at h * vdim; or null
+    int gate_ld;
+    void* out;                  // [rows][heads * vdim]
+};
+
+// out_h = sum_s o_s exp(m_s - M) / sum_s l_s exp(m_s - M) over the row's blocks of keys, times sigmoid(gate) if given
+template <typename T>
+__global__ void __launch_bounds__(128) talk_merge_kernel(MergeTalkArgs p) {
+    const int row = blockIdx.x, H = p.heads, vd = p.vdim;
+    const int seq = p.row_seq[row];
+    fr_pdl_wait();
+    fr_pdl_launch();
+    if (seq < 0) return;
+    const int pos = p.row_pos[row];
+    const int n = pos - max(0, pos - p.window + 1) + 1;
+    const int ns = (n + KS - 1) / KS;
+    const float* part = p.part + (size_t)row * p.splits * H * (vd + 2);
+    const size_t step = (size_t)H * (vd + 2);
+    for (int idx = threadIdx.x; idx < H * vd; idx += 128) {
+        const int h = idx / vd, d = idx - h * vd;
+        const float* ph = part + (size_t)h * (vd + 2);
+        float big = -INFINITY;
+        for (int s = 0; s < ns; ++s) big = fmaxf(big, ph[s * step + vd]);
+        float l = 0.f, o = 0.f;
+        for (int s = 0; s < ns; ++s) {
+            const float f = expf(ph[s * step + vd] - big);
+            l = fmaf(ph[s * step + vd + 1], f, l);
+            o = fmaf(ph[s * step + d], f, o);
+        }
+        o /= l;
+        if (p.gate != nullptr) {
+            const float g = fr_load((const T*)p.gate + (size_t)row * p.gate_ld + idx);
+            o *= 1.0f / (1.0f + expf(-g));
+        }
+        fr_store((T*)p.out + (size_t)row * H * vd + idx, o);
     }
 }
 
@@ -286,56 +327,415 @@ FR_EXPORT int attention_talk_store(void* src, int ld, int k_off, int v_off, int 
     return FR_OK;
 }
 
-// Floats that `scores` writes and `values` reads for n_rows rows: [rows][heads][stride], stride = the most keys a row sees,
-// rounded up to 4.
-FR_EXPORT long long attention_talk_stride(int window, int max_kv_len) {
+// Floats of scratch memory that `attention_talk_rows` needs for n_rows rows: what every block of KS keys of a row leaves.
+static int talk_splits(int window, int max_kv_len) {
     const int span = window > 0 && window < max_kv_len ? window : max_kv_len;
-    return (long long)((span + 3) / 4 * 4);
+    return span > 0 ? (span + KS - 1) / KS : 1;
 }
 
-FR_EXPORT int attention_talk_scores(const void* q, int q_ld, const void* k_pool, const int* table, int table_width, int page,
-                                    const int* row_seq, const int* row_pos, int n_rows, int heads, int kv_heads, int dim, int window,
-                                    int max_kv_len, float scale, const float* slopes, const void* talk, int talk_dtype, float* out,
-                                    int dtype, cudaStream_t stream) {
+FR_EXPORT long long attention_talk_scratch_floats(int n_rows, int heads, int vdim, int window, int max_kv_len) {
+    return (long long)n_rows * talk_splits(window, max_kv_len) * heads * (vdim + 2);
+}
+
+template <typename T, int VEC>
+static cudaError_t launch_split(const SplitArgs& p, dim3 grid, size_t smem, cudaStream_t stream) {
+    cudaError_t e = cudaFuncSetAttribute(talk_split_kernel<T, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    return fr_launch(talk_split_kernel<T, VEC>, grid, dim3(128), smem, stream, p);
+}
+
+// out [n_rows][heads * vdim]: every row's attention over the keys of its window, on the CUDA cores, in two launches: blocks of
+// KS keys, then their merge (with the gate).  q: [n_rows][q_ld], head h at h * dim; gate (or null): [n_rows][gate_ld].
+FR_EXPORT int attention_talk_rows(const void* q, int q_ld, const void* k_pool, const void* v_pool, const int* table, int table_width,
+                                  int page, const int* row_seq, const int* row_pos, int n_rows, int heads, int kv_heads, int dim, int vdim,
+                                  int window, int max_kv_len, float scale, const float* slopes, const void* talk, int talk_dtype,
+                                  const void* gate, int gate_ld, void* out, float* scratch, int dtype, cudaStream_t stream) {
     if (n_rows <= 0) return FR_OK;
-    if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || dim <= 0) FR_REFUSE("talk scores: %d heads on %d key heads of %d", heads, kv_heads, dim);
+    if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || dim <= 0 || vdim <= 0)
+        FR_REFUSE("talk attention: %d heads on %d key heads of %d and %d", heads, kv_heads, dim, vdim);
+    if (dtype != FR_F32 && dtype != FR_BF16) FR_REFUSE("talk attention: unknown dtype %d", dtype);
     if (window <= 0) window = max_kv_len;
-    ScoreArgs p;
-    p.q = q; p.q_ld = q_ld; p.k_pool = k_pool; p.table = table; p.table_width = table_width; p.page = page;
-    p.row_seq = row_seq; p.row_pos = row_pos; p.heads = heads; p.kv_heads = kv_heads; p.dim = dim; p.window = window;
-    p.stride = (int)attention_talk_stride(window, max_kv_len);
-    p.scale = scale; p.slopes = slopes; p.talk = FrVec{talk, talk_dtype}; p.out = out;
-    const size_t smem = ((size_t)heads * dim + (size_t)heads * KT + KT * (DC + 1) + (size_t)heads * heads) * sizeof(float);
-    if (smem > 200 * 1024) FR_REFUSE("talk scores: %d heads of %d need %zu bytes of shared memory", heads, dim, smem);
-    const dim3 grid((unsigned)((p.stride + KT - 1) / KT), (unsigned)n_rows);
-    if (dtype == FR_F32) {
-        FR_CUDA(cudaFuncSetAttribute(talk_scores_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        FR_CUDA(fr_launch(talk_scores_kernel<float>, grid, dim3(KT), smem, stream, p));
-    } else if (dtype == FR_BF16) {
-        FR_CUDA(cudaFuncSetAttribute(talk_scores_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        FR_CUDA(fr_launch(talk_scores_kernel<bf16>, grid, dim3(KT), smem, stream, p));
-    } else {
-        FR_REFUSE("talk scores: unknown dtype %d", dtype);
+    SplitArgs p;
+    p.q = q; p.q_ld = q_ld; p.k_pool = k_pool; p.v_pool = v_pool; p.table = table; p.table_width = table_width; p.page = page;
+    p.row_seq = row_seq; p.row_pos = row_pos; p.heads = heads; p.kv_heads = kv_heads; p.dim = dim; p.vdim = vdim; p.window = window;
+    p.splits = talk_splits(window, max_kv_len);
+    p.scale = scale; p.slopes = slopes; p.talk = FrVec{talk, talk_dtype}; p.part = scratch;
+    const size_t smem = ((size_t)KS + 2 * (size_t)heads * KS + (size_t)heads * dim + (size_t)heads * heads + 2 * (size_t)heads) * sizeof(float);
+    if (smem > 200 * 1024) FR_REFUSE("talk attention: %d heads of %d need %zu bytes of shared memory", heads, dim, smem);
+    const dim3 grid((unsigned)p.splits, (unsigned)n_rows);
+    const size_t esz = dtype == FR_F32 ? 4 : 2;
+    const bool aligned = ((uintptr_t)k_pool % 16) == 0 && ((size_t)dim * esz) % 16 == 0;
+    cudaError_t launched;
+    if (dtype == FR_F32) launched = aligned ? launch_split<float, 4>(p, grid, smem, stream) : launch_split<float, 1>(p, grid, smem, stream);
+    else launched = aligned ? launch_split<bf16, 8>(p, grid, smem, stream) : launch_split<bf16, 1>(p, grid, smem, stream);
+    FR_CUDA(launched);
+    FR_CHECK_LAUNCH("talk split");
+    MergeTalkArgs m;
+    m.part = scratch; m.row_seq = row_seq; m.row_pos = row_pos; m.heads = heads; m.vdim = vdim; m.window = window; m.splits = p.splits;
+    m.gate = gate; m.gate_ld = gate_ld; m.out = out;
+    if (dtype == FR_F32) FR_CUDA(fr_launch(talk_merge_kernel<float>, dim3(n_rows), dim3(128), 0, stream, m));
+    else FR_CUDA(fr_launch(talk_merge_kernel<bf16>, dim3(n_rows), dim3(128), 0, stream, m));
+    FR_CHECK_LAUNCH("talk merge");
+    return FR_OK;
+}
+
+// ------------------------------------------------------------------ bfloat16 prompts on the tensor cores
+// The mixed scores go through memory once, [row][head][stride] floats.  A row at position i sees the keys j0 = max(0, i -
+// window + 1) .. i; slot t of its stride is the key (j0 / 64) * 64 + t, so that a block of 64 keys (a page) starts at a
+// multiple of 64 slots in every row and 16-byte accesses stay aligned.
+namespace {
+
+constexpr int PB = 64;             // keys per block: a page of the cache
+constexpr int QR = 16;             // rows of a sequence per CTA of the score kernel
+constexpr int RAW_LD = 72;         // floats per (head, row) of a block's raw scores: 64 and a pad against bank conflicts
+
+static int prompt_stride(int window, int max_kv_len) {
+    const int all = (max_kv_len + PB - 1) / PB;
+    const int seen = window > 0 ? (window + PB - 1) / PB + 1 : all;
+    return (seen < all ? seen : all) * PB;
+}
+
+__device__ __forceinline__ void ldsm4(uint32_t (&r)[4], const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float x, float y) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(x, y);
+    return *(const uint32_t*)&v;
+}
+
+// head and remainder of two fp32 weights as packed bf16 pairs: w = hi + lo to 2^-17
+__device__ __forceinline__ void split_bf16(float x, float y, uint32_t& hi, uint32_t& lo) {
+    const bf16 hx = __float2bfloat16_rn(x), hy = __float2bfloat16_rn(y);
+    const __nv_bfloat162 h = __halves2bfloat162(hx, hy);
+    hi = *(const uint32_t*)&h;
+    lo = pack_bf16(x - __bfloat162float(hx), y - __bfloat162float(hy));
+}
+
+struct PromptArgs {
+    const bf16* q;              // [rows][q_ld], head h at h * dim
+    int q_ld;
+    const bf16* k_pool;         // [pages][64][kv_heads][dim]
+    const bf16* v_pool;         // [pages][64][kv_heads][vdim]
+    const int* table;
+    int table_width;
+    const int* seq_start;
+    const int* seq_qlen;
+    const int* seq_pos0;
+    int heads, kv_heads, dim, dkp, vdim, window, stride;
+    float scale;
+    const float* slopes;
+    FrVec talk;
+    const bf16* gate;
+    int gate_ld;
+    bf16* out;                  // [rows][heads * vdim]
+    float* mixed;               // [rows][heads][stride]
+};
+
+// 16 rows of a sequence, every head, the key blocks that any of the rows sees.  A warp owns 16 of a block's 64 keys: it
+// stages them for one key head at a time, multiplies with each query head of the group (A and B fragments by ldmatrix) and
+// leaves scale * q.k - slope * distance in shared memory; then the CTA mixes the heads (4 heads x 4 keys per thread and
+// step, the matrix transposed so that four heads' factors are one 16-byte read) and writes the mixed scores.
+__global__ void __launch_bounds__(128) talk_prompt_scores_kernel(PromptArgs p) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int H = p.heads, G = p.kv_heads, per = H / G, DKP = p.dkp, H4 = (H + 3) & ~3;
+    const int q_ld_s = H * DKP + 8, k_ld_s = DKP + 8;
+    float* raw = (float*)smem_raw;                                  // [H][QR][RAW_LD]
+    float* tkt = raw + (size_t)H * QR * RAW_LD;                     // [H][H4]: tkt[g][h] = talk[h][g]
+    bf16* sq = (bf16*)(tkt + (size_t)H * H4);                       // [QR][q_ld_s]
+    bf16* skw = sq + (size_t)QR * q_ld_s;                           // [4 warps][16][k_ld_s]
+    const int seq = blockIdx.y, q0 = blockIdx.x * QR;
+    const int qlen = p.seq_qlen[seq];
+    if (q0 >= qlen) return;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gid = lane >> 2, t4 = lane & 3;
+    const int n_rows = min(QR, qlen - q0);
+    fr_pdl_wait();
+    fr_pdl_launch();
+    const int row0 = p.seq_start[seq] + q0, pos0 = p.seq_pos0[seq] + q0, last_pos = pos0 + n_rows - 1;
+    for (int i = tid; i < H * H4; i += 128) {
+        const int g = i / H4, h = i - g * H4;
+        tkt[i] = h < H ? (p.talk.p != nullptr ? p.talk.at(h * H + g) : (h == g ? 1.f : 0.f)) : 0.f;
     }
-    FR_CHECK_LAUNCH("talk scores");
+    const int cpr = DKP / 8;                                         // 16-byte pieces per (row, head)
+    for (int idx = tid; idx < QR * H * cpr; idx += 128) {
+        const int r = idx / (H * cpr), rest = idx - r * H * cpr, h = rest / cpr, c = (rest - h * cpr) * 8;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < n_rows && c < p.dim) v = *(const uint4*)(p.q + (size_t)(row0 + r) * p.q_ld + (size_t)h * p.dim + c);
+        *(uint4*)(sq + (size_t)r * q_ld_s + h * DKP + c) = v;
+    }
+    __syncthreads();
+    const int lo0 = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int b_lo = lo0 / PB, b_hi = last_pos / PB;
+    const int* table = p.table + (size_t)seq * p.table_width;
+    bf16* sk = skw + (size_t)warp * 16 * k_ld_s;
+    const bf16* a_at = sq + (size_t)((lane & 7) + ((lane >> 3) & 1) * 8) * q_ld_s + (lane >> 4) * 8;
+    const bf16* b_at = sk + (size_t)((lane & 7) + (lane >> 4) * 8) * k_ld_s + ((lane >> 3) & 1) * 8;
+    for (int b = b_lo; b <= b_hi; ++b) {
+        const int page = table[b];
+        for (int g = 0; g < G; ++g) {
+            for (int idx = lane; idx < 16 * cpr; idx += 32) {
+                const int r = idx / cpr, c = (idx - r * cpr) * 8, key = warp * 16 + r;
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (b * PB + key <= last_pos && c < p.dim) v = *(const uint4*)(p.k_pool + (((size_t)page * PB + key) * G + g) * p.dim + c);
+                *(uint4*)(sk + (size_t)r * k_ld_s + c) = v;
+            }
+            __syncwarp();
+            for (int h = g * per; h < (g + 1) * per; ++h) {
+                float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+                for (int ks = 0; ks < DKP; ks += 16) {
+                    uint32_t a[4], kb[4];
+                    ldsm4(a, a_at + h * DKP + ks);
+                    ldsm4(kb, b_at + ks);
+                    mma_bf16(acc[0], a, kb[0], kb[1]);
+                    mma_bf16(acc[1], a, kb[2], kb[3]);
+                }
+                const float slope = p.slopes != nullptr ? p.slopes[h] : 0.f;
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        const int r = gid + 8 * half, col = warp * 16 + nt * 8 + 2 * t4;
+                        const float d0 = (float)(pos0 + r - (b * PB + col));
+                        float2 v;
+                        v.x = acc[nt][2 * half] * p.scale - slope * d0;
+                        v.y = acc[nt][2 * half + 1] * p.scale - slope * (d0 - 1.0f);
+                        *(float2*)(raw + ((size_t)h * QR + r) * RAW_LD + col) = v;
+                    }
+                }
+            }
+            __syncwarp();
+        }
+        __syncthreads();
+        // ---- mixing: an item is (4 heads, a row, 4 keys)
+        const int items = (H4 / 4) * QR * (PB / 4);
+        for (int it = tid; it < items; it += 128) {
+            const int k4 = (it % (PB / 4)) * 4, r = (it / (PB / 4)) % QR, h0 = (it / (PB / 4) / QR) * 4;
+            const int pos = pos0 + r;
+            if (r >= n_rows) continue;
+            const int first = p.window > 0 ? max(0, pos - p.window + 1) / PB : 0;
+            if (b < first || b > pos / PB) continue;                // the row sees nothing of this block
+            float4 m[4];
+#pragma unroll
+            for (int a = 0; a < 4; ++a) m[a] = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int g = 0; g < H; ++g) {
+                const float4 s = *(const float4*)(raw + ((size_t)g * QR + r) * RAW_LD + k4);
+                const float4 w = *(const float4*)(tkt + (size_t)g * H4 + h0);
+                const float wa[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                for (int a = 0; a < 4; ++a) {
+                    m[a].x = fmaf(wa[a], s.x, m[a].x);
+                    m[a].y = fmaf(wa[a], s.y, m[a].y);
+                    m[a].z = fmaf(wa[a], s.z, m[a].z);
+                    m[a].w = fmaf(wa[a], s.w, m[a].w);
+                }
+            }
+            float* dst = p.mixed + ((size_t)(row0 + r) * H + h0) * p.stride + (size_t)(b - first) * PB + k4;
+#pragma unroll
+            for (int a = 0; a < 4; ++a)
+                if (h0 + a < H) *(float4*)(dst + (size_t)a * p.stride) = m[a];
+        }
+        __syncthreads();
+    }
+}
+
+// 64 rows of a sequence and one head: the softmax of the mixed scores, block of keys by block of keys with a running
+// maximum and sum, and the weights times the values on the tensor cores.  A thread reads the scores of its places of the
+// accumulator layout straight from memory (16-byte pairs, issued before the values are staged); V is staged transposed.
+template <int DV>
+__global__ void __launch_bounds__(128, 2) talk_prompt_values_kernel(PromptArgs p) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    constexpr int BM = 64, PAD = 8;
+    bf16* svt = (bf16*)smem_raw;                                    // [DV][PB + PAD]
+    const int seq = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * BM;
+    const int qlen = p.seq_qlen[seq];
+    if (q0 >= qlen) return;
+    const int H = p.heads, G = p.kv_heads, vd = p.vdim;
+    const int kvh = h / (H / G);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int n_rows = min(BM, qlen - q0);
+    fr_pdl_wait();
+    fr_pdl_launch();
+    const int row0 = p.seq_start[seq] + q0, pos0 = p.seq_pos0[seq] + q0, last_pos = pos0 + n_rows - 1;
+    float o[DV / 8][4];
+#pragma unroll
+    for (int i = 0; i < DV / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    int my_pos[2], my_first[2];
+    const float* my_s[2];
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = warp * 16 + g + 8 * half;
+        my_pos[half] = r < n_rows ? pos0 + r : -1;                  // a row beyond the sequence's sees nothing
+        my_first[half] = p.window > 0 ? max(0, pos0 + r - p.window + 1) : 0;
+        my_s[half] = p.mixed + ((size_t)(row0 + min(r, n_rows - 1)) * H + h) * p.stride;
+    }
+    const int lo0 = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int* table = p.table + (size_t)seq * p.table_width;
+    for (int b = lo0 / PB; b <= last_pos / PB; ++b) {
+        const int page = table[b];
+        float s[PB / 8][4];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int pos = my_pos[half];
+            const bool any = pos >= 0 && b >= my_first[half] / PB && b <= pos / PB;
+            const float* src = my_s[half] + (ptrdiff_t)(b - my_first[half] / PB) * PB + 2 * t;
+#pragma unroll
+            for (int nt = 0; nt < PB / 8; ++nt) {
+                float2 v = make_float2(-INFINITY, -INFINITY);
+                if (any) {
+                    v = *(const float2*)(src + nt * 8);
+                    const int j = b * PB + nt * 8 + 2 * t;
+                    if (j > pos || j < my_first[half]) v.x = -INFINITY;
+                    if (j + 1 > pos || j + 1 < my_first[half]) v.y = -INFINITY;
+                }
+                s[nt][2 * half] = v.x;
+                s[nt][2 * half + 1] = v.y;
+            }
+        }
+        __syncthreads();                                            // the block before is done with svt
+        const bf16* vp = p.v_pool + ((size_t)page * PB * G + kvh) * vd;
+        for (int idx = tid; idx < PB * (DV / 8); idx += 128) {
+            const int r = idx % PB, c = (idx / PB) * 8;             // consecutive threads, consecutive keys: the 2-byte stores spread over the banks
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (b * PB + r <= last_pos && c < vd) v = *(const uint4*)(vp + (size_t)r * G * vd + c);
+            const bf16* e = (const bf16*)&v;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) svt[(c + i) * (PB + PAD) + r] = e[i];
+        }
+        __syncthreads();
+        float m_new[2] = {m_run[0], m_run[1]};
+#pragma unroll
+        for (int nt = 0; nt < PB / 8; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) m_new[e >> 1] = fmaxf(m_new[e >> 1], s[nt][e]);
+        float corr[2];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            m_new[half] = fmaxf(m_new[half], __shfl_xor_sync(0xffffffffu, m_new[half], 1));
+            m_new[half] = fmaxf(m_new[half], __shfl_xor_sync(0xffffffffu, m_new[half], 2));
+            corr[half] = m_new[half] == -INFINITY ? 1.f : expf(m_run[half] - m_new[half]);
+            m_run[half] = m_new[half];
+            l_run[half] *= corr[half];
+        }
+#pragma unroll
+        for (int i = 0; i < DV / 8; ++i) {
+            o[i][0] *= corr[0];
+            o[i][1] *= corr[0];
+            o[i][2] *= corr[1];
+            o[i][3] *= corr[1];
+        }
+#pragma unroll
+        for (int nt = 0; nt < PB / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int half = e >> 1;
+                const float w = m_new[half] == -INFINITY ? 0.f : expf(s[nt][e] - m_new[half]);
+                s[nt][e] = w;
+                l_run[half] += w;
+            }
+        }
+#pragma unroll
+        for (int kk = 0; kk < PB / 16; ++kk) {
+            uint32_t hi[4], lw[4];
+            split_bf16(s[2 * kk][0], s[2 * kk][1], hi[0], lw[0]);
+            split_bf16(s[2 * kk][2], s[2 * kk][3], hi[1], lw[1]);
+            split_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1], hi[2], lw[2]);
+            split_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3], hi[3], lw[3]);
+#pragma unroll
+            for (int nt = 0; nt < DV / 8; ++nt) {
+                const bf16* vb = svt + (nt * 8 + g) * (PB + PAD) + kk * 16 + 2 * t;
+                const uint32_t b0 = *(const uint32_t*)vb, b1 = *(const uint32_t*)(vb + 8);
+                mma_bf16(o[nt], hi, b0, b1);
+                mma_bf16(o[nt], lw, b0, b1);
+            }
+        }
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        l_run[half] += __shfl_xor_sync(0xffffffffu, l_run[half], 1);
+        l_run[half] += __shfl_xor_sync(0xffffffffu, l_run[half], 2);
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = warp * 16 + g + 8 * half;
+        if (r >= n_rows) continue;
+        const float inv = l_run[half] > 0.f ? 1.0f / l_run[half] : 0.f;
+        bf16* dst = p.out + (size_t)(row0 + r) * H * vd + (size_t)h * vd;
+        const bf16* gate = p.gate != nullptr ? p.gate + (size_t)(row0 + r) * p.gate_ld + (size_t)h * vd : nullptr;
+#pragma unroll
+        for (int nt = 0; nt < DV / 8; ++nt) {
+            const int c = nt * 8 + 2 * t;
+            if (c >= vd) continue;                                   // vd is even: c + 1 < vd as well
+            float x = o[nt][2 * half] * inv, y = o[nt][2 * half + 1] * inv;
+            if (gate != nullptr) {
+                const __nv_bfloat162 gv = *(const __nv_bfloat162*)(gate + c);
+                x *= 1.0f / (1.0f + expf(-__low2float(gv)));
+                y *= 1.0f / (1.0f + expf(-__high2float(gv)));
+            }
+            *(uint32_t*)(dst + c) = pack_bf16(x, y);
+        }
+    }
+}
+
+template <int DV>
+int launch_values(const PromptArgs& p, int n_seqs, int max_q_len, cudaStream_t stream) {
+    const size_t smem = (size_t)DV * (PB + 8) * sizeof(bf16);
+    FR_CUDA(cudaFuncSetAttribute(talk_prompt_values_kernel<DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const dim3 grid((unsigned)((max_q_len + 63) / 64), (unsigned)p.heads, (unsigned)n_seqs);
+    FR_CUDA(fr_launch(talk_prompt_values_kernel<DV>, grid, dim3(128), smem, stream, p));
+    FR_CHECK_LAUNCH("talk prompt values");
     return FR_OK;
 }
 
-FR_EXPORT int attention_talk_values(const float* scores, const void* v_pool, const int* table, int table_width, int page,
-                                    const int* row_seq, const int* row_pos, int n_rows, int heads, int kv_heads, int vdim, int window,
-                                    int max_kv_len, const void* gate, int gate_ld, void* out, int dtype, cudaStream_t stream) {
-    if (n_rows <= 0) return FR_OK;
-    if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || vdim <= 0) FR_REFUSE("talk values: %d heads on %d value heads of %d", heads, kv_heads, vdim);
-    if (window <= 0) window = max_kv_len;
-    ValueArgs p;
-    p.scores = scores; p.v_pool = v_pool; p.table = table; p.table_width = table_width; p.page = page; p.row_seq = row_seq;
-    p.row_pos = row_pos; p.heads = heads; p.kv_heads = kv_heads; p.vdim = vdim; p.window = window;
-    p.stride = (int)attention_talk_stride(window, max_kv_len);
-    p.gate = gate; p.gate_ld = gate_ld; p.out = out;
-    const dim3 grid((unsigned)n_rows, (unsigned)kv_heads);
-    if (dtype == FR_F32) FR_CUDA(fr_launch(talk_values_kernel<float>, grid, dim3(128), 0, stream, p));
-    else if (dtype == FR_BF16) FR_CUDA(fr_launch(talk_values_kernel<bf16>, grid, dim3(128), 0, stream, p));
-    else FR_REFUSE("talk values: unknown dtype %d", dtype);
-    FR_CHECK_LAUNCH("talk values");
-    return FR_OK;
+size_t prompt_scores_smem(int heads, int dim) {
+    const int dkp = (dim + 15) / 16 * 16, h4 = (heads + 3) & ~3;
+    return ((size_t)heads * QR * RAW_LD + (size_t)heads * h4) * sizeof(float) +
+           ((size_t)QR * (heads * dkp + 8) + (size_t)4 * 16 * (dkp + 8)) * sizeof(bf16);
+}
+
+}  // namespace
+
+// Floats of scratch memory for the mixed scores of n_rows rows; 0 if the tensor-core kernels do not take these sizes
+// (key channels in eights, value channels in eights up to 128, what the score kernel holds in shared memory).
+FR_EXPORT long long attention_talk_prompt_scratch_floats(int n_rows, int heads, int dim, int vdim, int window, int max_kv_len) {
+    if (heads <= 0 || dim <= 0 || dim % 8 || vdim <= 0 || vdim % 8 || vdim > 128 || heads > 65535) return 0;
+    if (prompt_scores_smem(heads, dim) > 200 * 1024) return 0;
+    return (long long)n_rows * heads * prompt_stride(window, max_kv_len);
+}
+
+// bf16; pages of 64.  Sequences bring seq_qlen rows from row seq_start, the first at position seq_pos0; their keys and values
+// are in the cache already.  q: [n_rows][q_ld], head h at h * dim; gate (or null): [n_rows][gate_ld]; out [n_rows][heads * vdim].
+FR_EXPORT int attention_talk_prompt(const void* q, int q_ld, const void* k_pool, const void* v_pool, const int* table, int table_width,
+                                    int page, const int* seq_start, const int* seq_qlen, const int* seq_pos0, int n_seqs, int n_rows,
+                                    int max_q_len, int heads, int kv_heads, int dim, int vdim, int window, int max_kv_len, float scale,
+                                    const float* slopes, const void* talk, int talk_dtype, const void* gate, int gate_ld, void* out,
+                                    float* scratch, cudaStream_t stream) {
+    if (n_seqs <= 0 || n_rows <= 0 || max_q_len <= 0) return FR_OK;
+    if (page != PB) FR_REFUSE("talk prompt: pages of %d (64)", page);
+    if (kv_heads <= 0 || heads % kv_heads) FR_REFUSE("talk prompt: %d heads cannot share %d key/value heads", heads, kv_heads);
+    if (attention_talk_prompt_scratch_floats(n_rows, heads, dim, vdim, window, max_kv_len) <= 0)
+        FR_REFUSE("talk prompt: %d heads of %d and %d are not sizes the tensor-core kernels take", heads, dim, vdim);
+    if (n_seqs > 65535) FR_REFUSE("talk prompt: %d sequences", n_seqs);
+    if ((uintptr_t)q % 16 || q_ld % 8 || (uintptr_t)k_pool % 16 || (uintptr_t)v_pool % 16 || (gate != nullptr && ((uintptr_t)gate % 4 || gate_ld % 2)))
+        FR_REFUSE("talk prompt: rows and pools must start at 16 bytes");
+    PromptArgs p;
+    p.q = (const bf16*)q; p.q_ld = q_ld; p.k_pool = (const bf16*)k_pool; p.v_pool = (const bf16*)v_pool; p.table = table;
+    p.table_width = table_width; p.seq_start = seq_start; p.seq_qlen = seq_qlen; p.seq_pos0 = seq_pos0; p.heads = heads;
+    p.kv_heads = kv_heads; p.dim = dim; p.dkp = (dim + 15) / 16 * 16; p.vdim = vdim; p.window = window;
+    p.stride = prompt_stride(window, max_kv_len); p.scale = scale; p.slopes = slopes; p.talk = FrVec{talk, talk_dtype};
+    p.gate = (const bf16*)gate; p.gate_ld = gate_ld; p.out = (bf16*)out; p.mixed = scratch;
+    const size_t smem = prompt_scores_smem(heads, dim);
+    FR_CUDA(cudaFuncSetAttribute(talk_prompt_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    FR_CUDA(fr_launch(talk_prompt_scores_kernel, dim3((unsigned)((max_q_len + QR - 1) / QR), (unsigned)n_seqs), dim3(128), smem, stream, p));
+    FR_CHECK_LAUNCH("talk prompt scores");
+    if (vdim <= 32) return launch_values<32>(p, n_seqs, max_q_len, stream);
+    if (vdim <= 64) return launch_values<64>(p, n_seqs, max_q_len, stream);
+    return launch_values<128>(p, n_seqs, max_q_len, stream);
 }

@@ -118,8 +118,9 @@ FAMILY(Routed, routed, "routed", resolve(h, fam, "routed_route", t.route);
        resolve(h, fam, "routed_sort_pairs", t.sort_pairs); resolve(h, fam, "routed_combine", t.combine);
        resolve(h, fam, "routed_route_scored", t.route_scored);)
 FAMILY(AttentionTalk, attention_talk, "attention_talk", resolve(h, fam, "attention_talk_store", t.store);
-       resolve(h, fam, "attention_talk_stride", t.stride); resolve(h, fam, "attention_talk_scores", t.scores);
-       resolve(h, fam, "attention_talk_values", t.values);)
+       resolve(h, fam, "attention_talk_scratch_floats", t.scratch_floats); resolve(h, fam, "attention_talk_rows", t.rows);
+       resolve(h, fam, "attention_talk_prompt_scratch_floats", t.prompt_scratch_floats);
+       resolve(h, fam, "attention_talk_prompt", t.prompt);)
 FAMILY(Delta, delta, "delta", resolve(h, fam, "delta_conv_prepare", t.conv_prepare);
        resolve(h, fam, "delta_conv_state", t.conv_state); resolve(h, fam, "delta_scan", t.scan);)
 FAMILY(AttentionLatent, attention_latent, "attention_latent", resolve(h, fam, "attention_latent_rotate_pairs", t.rotate_pairs);

@@ -125,11 +125,12 @@ struct AttentionTalk {
     last_error_fn last_error;
     int (*store)(void*, int, int, int, int, int, int, const int*, const int*, void*, void*, const int*, int, int, int, int, const void*,
                  const void*, int, void*, cudaStream_t);
-    long long (*stride)(int, int);
-    int (*scores)(const void*, int, const void*, const int*, int, int, const int*, const int*, int, int, int, int, int, int, float,
-                  const float*, const void*, int, float*, int, cudaStream_t);
-    int (*values)(const float*, const void*, const int*, int, int, const int*, const int*, int, int, int, int, int, int, const void*, int,
-                  void*, int, cudaStream_t);
+    long long (*scratch_floats)(int, int, int, int, int);
+    int (*rows)(const void*, int, const void*, const void*, const int*, int, int, const int*, const int*, int, int, int, int, int, int, int,
+                float, const float*, const void*, int, const void*, int, void*, float*, int, cudaStream_t);
+    long long (*prompt_scratch_floats)(int, int, int, int, int, int);
+    int (*prompt)(const void*, int, const void*, const void*, const int*, int, int, const int*, const int*, const int*, int, int, int, int,
+                  int, int, int, int, int, float, const float*, const void*, int, const void*, int, void*, float*, cudaStream_t);
 };
 struct AttentionMma {
     last_error_fn last_error;

@@ -309,6 +309,15 @@ void Ops::two_sided_act(Tensor& z, const Tensor& pq) {
 }
 
 // ------------------------------------------------------------------ attention whose heads talk before the softmax
+// FRIDAY_TALK_PROMPT=0 sends prompts through the CUDA-core kernels too (for comparisons)
+static bool talk_prompt_allowed() {
+    static const bool on = [] {
+        const char* e = getenv("FRIDAY_TALK_PROMPT");
+        return !(e != nullptr && e[0] == '0');
+    }();
+    return on;
+}
+
 void Ops::talk_store(Tensor& proj, const TalkSpec& s, const CacheView& view, const StepContext& ctx, const Tensor* blend,
                      const Tensor* lambda, Tensor* keep) {
     if (view.kind != CacheRequest::KV || !view.k_pool) throw KernelError("talk_store needs a view of keys and values");
@@ -335,27 +344,42 @@ Tensor Ops::talk_attention(const Tensor& proj, const TalkSpec& s, const CacheVie
     const auto& k = kernels::attention_talk();
     const int64_t rows = proj.rows();
     Tensor out = alloc(proj.dtype, rows, (int64_t)s.heads * s.vdim);
-    const long long stride = k.stride(s.window, ctx.max_kv_len);
-    // the mixed scores of all heads go through memory, [rows][heads][stride] floats: rows are taken in runs that keep it
-    // below a gigabyte
-    const int64_t per_row = (int64_t)s.heads * stride;
-    int64_t run = std::max<int64_t>(1, ((int64_t)1 << 28) / std::max<int64_t>(per_row, 1));
-    run = std::min(run, rows);
-    float* scores = scratch_floats(run * per_row);
     const char* q = (const char*)proj.data + (size_t)s.q_off * dtype_size(proj.dtype);
     const char* gate = s.gate_off >= 0 ? (const char*)proj.data + (size_t)s.gate_off * dtype_size(proj.dtype) : nullptr;
     const size_t row_bytes = (size_t)proj.ld * dtype_size(proj.dtype);
+    // Prompts in bfloat16 whose sizes the tensor-core kernels take: the mixed scores of all heads go through memory once
+    // ([rows][heads][keys in sight] floats), the products run on the tensor cores.
+    if (proj.dtype == DType::BF16 && !ctx.decode && ctx.n_seqs > 0 && ctx.rows == (int)rows && ctx.max_q_len >= 16 &&
+        view.page_size == 64 && talk_prompt_allowed()) {
+        const long long need = k.prompt_scratch_floats((int)rows, s.heads, s.dim, s.vdim, s.window, ctx.max_kv_len);
+        const bool fits = need > 0 && need <= ((long long)1 << 29) && proj.ld % 8 == 0 && s.q_off % 8 == 0 && (s.gate_off < 0 || s.gate_off % 2 == 0);
+        if (fits) {
+            float* scratch = scratch_floats(need);
+            Timed t(*this, Attention);
+            call(launches_, k, k.prompt(q, (int)proj.ld, view.k_pool, view.v_pool, view.block_table, view.table_width, view.page_size,
+                                        ctx.seq_start, ctx.seq_qlen, ctx.seq_pos0, ctx.n_seqs, (int)rows, ctx.max_q_len, s.heads, s.kv_heads,
+                                        s.dim, s.vdim, s.window, ctx.max_kv_len, s.scale, s.slopes, s.talk ? s.talk->data : nullptr,
+                                        s.talk ? code(s.talk->dtype) : 0, gate, (int)proj.ld, out.data, scratch, stream_), "talk_prompt");
+            ++launches_;
+            return out;
+        }
+    }
+    // everything else: a row's keys in blocks, every block with all heads, then their merge; rows are taken in runs that
+    // keep what the blocks leave below a gigabyte
+    const int64_t per_row = std::max<int64_t>(1, k.scratch_floats(1, s.heads, s.vdim, s.window, ctx.max_kv_len));
+    int64_t run = std::max<int64_t>(1, ((int64_t)1 << 28) / per_row);
+    run = std::min(run, rows);
+    float* scratch = scratch_floats(run * per_row);
     for (int64_t r0 = 0; r0 < rows; r0 += run) {
         const int n = (int)std::min(run, rows - r0);
         Timed t(*this, Attention);
-        call(launches_, k, k.scores(q + r0 * row_bytes, (int)proj.ld, view.k_pool, view.block_table, view.table_width, view.page_size,
-                                    ctx.row_seq + r0, ctx.row_pos + r0, n, s.heads, s.kv_heads, s.dim, s.window, ctx.max_kv_len, s.scale,
-                                    s.slopes, s.talk ? s.talk->data : nullptr, s.talk ? code(s.talk->dtype) : 0, scores, code(proj.dtype),
-                                    stream_), "talk_scores");
-        call(launches_, k, k.values(scores, view.v_pool, view.block_table, view.table_width, view.page_size, ctx.row_seq + r0,
-                                    ctx.row_pos + r0, n, s.heads, s.kv_heads, s.vdim, s.window, ctx.max_kv_len,
-                                    gate ? gate + r0 * row_bytes : nullptr, (int)proj.ld,
-                                    (char*)out.data + (size_t)r0 * out.ld * dtype_size(out.dtype), code(proj.dtype), stream_), "talk_values");
+        call(launches_, k, k.rows(q + r0 * row_bytes, (int)proj.ld, view.k_pool, view.v_pool, view.block_table, view.table_width,
+                                  view.page_size, ctx.row_seq + r0, ctx.row_pos + r0, n, s.heads, s.kv_heads, s.dim, s.vdim, s.window,
+                                  ctx.max_kv_len, s.scale, s.slopes, s.talk ? s.talk->data : nullptr, s.talk ? code(s.talk->dtype) : 0,
+                                  gate ? gate + r0 * row_bytes : nullptr, (int)proj.ld,
+                                  (char*)out.data + (size_t)r0 * out.ld * dtype_size(out.dtype), scratch, code(proj.dtype), stream_),
+             "talk_rows");
+        ++launches_;
     }
     return out;
 }
