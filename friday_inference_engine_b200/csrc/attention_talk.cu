@@ -387,17 +387,11 @@ namespace {
 
 constexpr int PB = 64;             // keys per block: a page of the cache
 constexpr int QR = 16;             // rows of a sequence per CTA of the score kernel
-constexpr int RAW_LD = 72;         // floats per (head, row) of a block's raw scores: 64 and a pad against bank conflicts
 
 static int prompt_stride(int window, int max_kv_len) {
     const int all = (max_kv_len + PB - 1) / PB;
     const int seen = window > 0 ? (window + PB - 1) / PB + 1 : all;
     return (seen < all ? seen : all) * PB;
-}
-
-__device__ __forceinline__ void ldsm4(uint32_t (&r)[4], const void* p) {
-    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
 }
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -429,7 +423,7 @@ struct PromptArgs {
     const int* seq_start;
     const int* seq_qlen;
     const int* seq_pos0;
-    int heads, kv_heads, dim, dkp, vdim, window, stride;
+    int heads, kv_heads, dim, q_ld_s, vdim, window, stride;
     float scale;
     const float* slopes;
     FrVec talk;
@@ -439,120 +433,142 @@ struct PromptArgs {
     float* mixed;               // [rows][heads][stride]
 };
 
-// 16 rows of a sequence, every head, the key blocks that any of the rows sees.  A warp owns 16 of a block's 64 keys: it
-// stages them for one key head at a time, multiplies with each query head of the group (A and B fragments by ldmatrix) and
-// leaves scale * q.k - slope * distance in shared memory; then the CTA mixes the heads (4 heads x 4 keys per thread and
-// step, the matrix transposed so that four heads' factors are one 16-byte read) and writes the mixed scores.
-__global__ void __launch_bounds__(128) talk_prompt_scores_kernel(PromptArgs p) {
+// 16 rows of a sequence, one block of 64 keys, every head.  The rows' queries are staged once for all heads; each of the
+// eight warps owns 8 of the keys and keeps scale * q.k - slope * distance of all heads in its accumulators (m16n8k16 with
+// the channels of a group of 32 dealt out so that a thread's 16-byte read of a query row and of its key are its A and B
+// fragments of two steps: a product does not care in which order its channels are summed, only that A and B agree).
+// The heads are then mixed in the registers, the matrix read from shared memory, and the mixed scores stored.
+template <int HP>
+__global__ void __launch_bounds__(256) talk_prompt_scores_kernel(PromptArgs p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    const int H = p.heads, G = p.kv_heads, per = H / G, DKP = p.dkp, H4 = (H + 3) & ~3;
-    const int q_ld_s = H * DKP + 8, k_ld_s = DKP + 8;
-    float* raw = (float*)smem_raw;                                  // [H][QR][RAW_LD]
-    float* tkt = raw + (size_t)H * QR * RAW_LD;                     // [H][H4]: tkt[g][h] = talk[h][g]
-    bf16* sq = (bf16*)(tkt + (size_t)H * H4);                       // [QR][q_ld_s]
-    bf16* skw = sq + (size_t)QR * q_ld_s;                           // [4 warps][16][k_ld_s]
-    const int seq = blockIdx.y, q0 = blockIdx.x * QR;
+    const int H = p.heads, per = H / p.kv_heads, dim = p.dim, G = p.kv_heads;
+    const int lq = p.q_ld_s;
+    float* tk = (float*)smem_raw;                                   // [HP][HP]: tk[h][g] = talk[h][g], zeros beyond H
+    float* sl = tk + HP * HP;                                       // [HP] slopes
+    bf16* sq = (bf16*)(sl + HP);                                    // [QR][lq]
+    const int seq = blockIdx.z, q0 = blockIdx.y * QR;
     const int qlen = p.seq_qlen[seq];
     if (q0 >= qlen) return;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gid = lane >> 2, t4 = lane & 3;
     const int n_rows = min(QR, qlen - q0);
+    const int pos0 = p.seq_pos0[seq] + q0, last_pos = pos0 + n_rows - 1;
+    const int lo0 = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int b = lo0 / PB + blockIdx.x;
+    if (b > last_pos / PB) return;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gid = lane >> 2, t4 = lane & 3;
+    for (int i = tid; i < HP * HP; i += 256) {
+        const int h = i / HP, g = i - h * HP;
+        tk[i] = (h < H && g < H) ? (p.talk.p != nullptr ? p.talk.at(h * H + g) : (h == g ? 1.f : 0.f)) : 0.f;
+    }
+    for (int i = tid; i < HP; i += 256) sl[i] = (i < H && p.slopes != nullptr) ? p.slopes[i] : 0.f;
     fr_pdl_wait();
     fr_pdl_launch();
-    const int row0 = p.seq_start[seq] + q0, pos0 = p.seq_pos0[seq] + q0, last_pos = pos0 + n_rows - 1;
-    for (int i = tid; i < H * H4; i += 128) {
-        const int g = i / H4, h = i - g * H4;
-        tkt[i] = h < H ? (p.talk.p != nullptr ? p.talk.at(h * H + g) : (h == g ? 1.f : 0.f)) : 0.f;
-    }
-    const int cpr = DKP / 8;                                         // 16-byte pieces per (row, head)
-    for (int idx = tid; idx < QR * H * cpr; idx += 128) {
-        const int r = idx / (H * cpr), rest = idx - r * H * cpr, h = rest / cpr, c = (rest - h * cpr) * 8;
+    const int row0 = p.seq_start[seq] + q0;
+    const int cpr = H * dim / 8;                                     // 16-byte pieces per row
+    for (int idx = tid; idx < QR * cpr; idx += 256) {
+        const int r = idx / cpr, c = (idx - r * cpr) * 8;
         uint4 v = make_uint4(0, 0, 0, 0);
-        if (r < n_rows && c < p.dim) v = *(const uint4*)(p.q + (size_t)(row0 + r) * p.q_ld + (size_t)h * p.dim + c);
-        *(uint4*)(sq + (size_t)r * q_ld_s + h * DKP + c) = v;
+        if (r < n_rows) v = *(const uint4*)(p.q + (size_t)(row0 + r) * p.q_ld + c);
+        *(uint4*)(sq + (size_t)r * lq + c) = v;
     }
     __syncthreads();
-    const int lo0 = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
-    const int b_lo = lo0 / PB, b_hi = last_pos / PB;
-    const int* table = p.table + (size_t)seq * p.table_width;
-    bf16* sk = skw + (size_t)warp * 16 * k_ld_s;
-    const bf16* a_at = sq + (size_t)((lane & 7) + ((lane >> 3) & 1) * 8) * q_ld_s + (lane >> 4) * 8;
-    const bf16* b_at = sk + (size_t)((lane & 7) + (lane >> 4) * 8) * k_ld_s + ((lane >> 3) & 1) * 8;
-    for (int b = b_lo; b <= b_hi; ++b) {
-        const int page = table[b];
-        for (int g = 0; g < G; ++g) {
-            for (int idx = lane; idx < 16 * cpr; idx += 32) {
-                const int r = idx / cpr, c = (idx - r * cpr) * 8, key = warp * 16 + r;
-                uint4 v = make_uint4(0, 0, 0, 0);
-                if (b * PB + key <= last_pos && c < p.dim) v = *(const uint4*)(p.k_pool + (((size_t)page * PB + key) * G + g) * p.dim + c);
-                *(uint4*)(sk + (size_t)r * k_ld_s + c) = v;
-            }
-            __syncwarp();
-            for (int h = g * per; h < (g + 1) * per; ++h) {
-                float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-                for (int ks = 0; ks < DKP; ks += 16) {
-                    uint32_t a[4], kb[4];
-                    ldsm4(a, a_at + h * DKP + ks);
-                    ldsm4(kb, b_at + ks);
-                    mma_bf16(acc[0], a, kb[0], kb[1]);
-                    mma_bf16(acc[1], a, kb[2], kb[3]);
+    const int page = p.table[(size_t)seq * p.table_width + b];
+    const int key = b * PB + warp * 8 + gid;                        // the key whose channels this thread reads
+    const bf16* krow = p.k_pool + ((size_t)page * PB + warp * 8 + gid) * G * dim;
+    const bool key_ok = key <= last_pos;
+    const bf16* qa_row = sq + (size_t)gid * lq + t4 * 8;
+    const bf16* qb_row = qa_row + (size_t)8 * lq;
+    float acc[HP][4];
+#pragma unroll
+    for (int h = 0; h < HP; ++h) acc[h][0] = acc[h][1] = acc[h][2] = acc[h][3] = 0.f;
+    const int nch = (dim + 31) / 32;
+    for (int c = 0; c < nch; ++c) {
+        const int ch = c * 32 + t4 * 8;                             // this thread's eight channels of the group
+        const bool ch_ok = ch < dim;
+        uint4 kf = make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int h = 0; h < HP; ++h) {
+            if (h < H) {
+                if (h % per == 0) {
+                    kf = make_uint4(0, 0, 0, 0);
+                    if (key_ok && ch_ok) kf = *(const uint4*)(krow + (size_t)(h / per) * dim + ch);
                 }
-                const float slope = p.slopes != nullptr ? p.slopes[h] : 0.f;
+                uint4 qa = make_uint4(0, 0, 0, 0), qb = qa;
+                if (ch_ok) {
+                    qa = *(const uint4*)(qa_row + (size_t)h * dim + c * 32);
+                    qb = *(const uint4*)(qb_row + (size_t)h * dim + c * 32);
+                }
+                const uint32_t a1[4] = {qa.x, qb.x, qa.y, qb.y}, a2[4] = {qa.z, qb.z, qa.w, qb.w};
+                mma_bf16(acc[h], a1, kf.x, kf.y);
+                mma_bf16(acc[h], a2, kf.z, kf.w);
+            }
+        }
+    }
+    // accumulator places: (row gid, keys 2 t4 and 2 t4 + 1), (row gid + 8, the same keys)
+    const int col = warp * 8 + 2 * t4;
+    const float d0 = (float)(pos0 + gid - (b * PB + col));          // row gid's distance to its first key; row gid + 8: d0 + 8
 #pragma unroll
-                for (int nt = 0; nt < 2; ++nt) {
+    for (int h = 0; h < HP; ++h) {
+        const float s = sl[h];
+        acc[h][0] = acc[h][0] * p.scale - s * d0;
+        acc[h][1] = acc[h][1] * p.scale - s * (d0 - 1.0f);
+        acc[h][2] = acc[h][2] * p.scale - s * (d0 + 8.0f);
+        acc[h][3] = acc[h][3] * p.scale - s * (d0 + 7.0f);
+    }
+    float* dst[2];
+    bool live[2];
 #pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        const int r = gid + 8 * half, col = warp * 16 + nt * 8 + 2 * t4;
-                        const float d0 = (float)(pos0 + r - (b * PB + col));
-                        float2 v;
-                        v.x = acc[nt][2 * half] * p.scale - slope * d0;
-                        v.y = acc[nt][2 * half + 1] * p.scale - slope * (d0 - 1.0f);
-                        *(float2*)(raw + ((size_t)h * QR + r) * RAW_LD + col) = v;
+    for (int half = 0; half < 2; ++half) {
+        const int r = gid + 8 * half, pos = pos0 + r;
+        const int first = p.window > 0 ? max(0, pos - p.window + 1) / PB : 0;
+        live[half] = r < n_rows && b >= first && b <= pos / PB;     // else the row sees nothing of this block
+        dst[half] = p.mixed + (size_t)(row0 + r) * H * p.stride + (ptrdiff_t)(b - first) * PB + col;
+    }
+    const bool mix = p.talk.p != nullptr;
+#pragma unroll
+    for (int h = 0; h < HP; ++h) {
+        if (h < H) {
+            float m[4] = {acc[h][0], acc[h][1], acc[h][2], acc[h][3]};
+            if (mix) {
+                m[0] = m[1] = m[2] = m[3] = 0.f;
+#pragma unroll
+                for (int g4 = 0; g4 < HP; g4 += 4) {
+                    const float4 w = *(const float4*)(tk + h * HP + g4);
+                    const float wa[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                    for (int a = 0; a < 4; ++a) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) m[e] = fmaf(wa[a], acc[g4 + a][e], m[e]);
                     }
                 }
             }
-            __syncwarp();
+            if (live[0]) *(float2*)(dst[0] + (size_t)h * p.stride) = make_float2(m[0], m[1]);
+            if (live[1]) *(float2*)(dst[1] + (size_t)h * p.stride) = make_float2(m[2], m[3]);
         }
-        __syncthreads();
-        // ---- mixing: an item is (4 heads, a row, 4 keys)
-        const int items = (H4 / 4) * QR * (PB / 4);
-        for (int it = tid; it < items; it += 128) {
-            const int k4 = (it % (PB / 4)) * 4, r = (it / (PB / 4)) % QR, h0 = (it / (PB / 4) / QR) * 4;
-            const int pos = pos0 + r;
-            if (r >= n_rows) continue;
-            const int first = p.window > 0 ? max(0, pos - p.window + 1) / PB : 0;
-            if (b < first || b > pos / PB) continue;                // the row sees nothing of this block
-            float4 m[4];
-#pragma unroll
-            for (int a = 0; a < 4; ++a) m[a] = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int g = 0; g < H; ++g) {
-                const float4 s = *(const float4*)(raw + ((size_t)g * QR + r) * RAW_LD + k4);
-                const float4 w = *(const float4*)(tkt + (size_t)g * H4 + h0);
-                const float wa[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-                for (int a = 0; a < 4; ++a) {
-                    m[a].x = fmaf(wa[a], s.x, m[a].x);
-                    m[a].y = fmaf(wa[a], s.y, m[a].y);
-                    m[a].z = fmaf(wa[a], s.z, m[a].z);
-                    m[a].w = fmaf(wa[a], s.w, m[a].w);
-                }
-            }
-            float* dst = p.mixed + ((size_t)(row0 + r) * H + h0) * p.stride + (size_t)(b - first) * PB + k4;
-#pragma unroll
-            for (int a = 0; a < 4; ++a)
-                if (h0 + a < H) *(float4*)(dst + (size_t)a * p.stride) = m[a];
-        }
-        __syncthreads();
     }
 }
 
+__device__ __forceinline__ void ldsm4_trans(uint32_t (&r)[4], const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, int src_bytes) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 // 64 rows of a sequence and one head: the softmax of the mixed scores, block of keys by block of keys with a running
 // maximum and sum, and the weights times the values on the tensor cores.  A thread reads the scores of its places of the
-// accumulator layout straight from memory (16-byte pairs, issued before the values are staged); V is staged transposed.
+// accumulator layout straight from memory (8-byte pairs), a block ahead of their use; the values of the next block arrive
+// by cp.async in the other of two buffers meanwhile, as they lie in the cache ([key][channel]); ldmatrix.trans makes the
+// B fragments of them.
 template <int DV>
 __global__ void __launch_bounds__(128, 2) talk_prompt_values_kernel(PromptArgs p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    constexpr int BM = 64, PAD = 8;
-    bf16* svt = (bf16*)smem_raw;                                    // [DV][PB + PAD]
+    constexpr int BM = 64, LV = DV + 8;
+    bf16* sv = (bf16*)smem_raw;                                     // [2][PB][LV]
     const int seq = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * BM;
     const int qlen = p.seq_qlen[seq];
     if (q0 >= qlen) return;
@@ -574,87 +590,118 @@ __global__ void __launch_bounds__(128, 2) talk_prompt_values_kernel(PromptArgs p
         const int r = warp * 16 + g + 8 * half;
         my_pos[half] = r < n_rows ? pos0 + r : -1;                  // a row beyond the sequence's sees nothing
         my_first[half] = p.window > 0 ? max(0, pos0 + r - p.window + 1) : 0;
-        my_s[half] = p.mixed + ((size_t)(row0 + min(r, n_rows - 1)) * H + h) * p.stride;
+        my_s[half] = p.mixed + ((size_t)(row0 + min(r, n_rows - 1)) * H + h) * p.stride + 2 * t;
     }
+    // what the warp's 16 rows see, in blocks: others are skipped by the whole warp
+    const int w_lo = (p.window > 0 ? max(0, pos0 + warp * 16 - p.window + 1) : 0) / PB;
+    const int w_hi = min(pos0 + warp * 16 + 15, last_pos) / PB;
+    const bool w_any = warp * 16 < n_rows;
     const int lo0 = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int b_lo = lo0 / PB, b_hi = last_pos / PB;
     const int* table = p.table + (size_t)seq * p.table_width;
-    for (int b = lo0 / PB; b <= last_pos / PB; ++b) {
-        const int page = table[b];
-        float s[PB / 8][4];
+
+    auto stage = [&](int b, int buf) {
+        const bf16* vp = p.v_pool + ((size_t)table[b] * PB * G + kvh) * vd;
+        bf16* dst = sv + (size_t)buf * PB * LV;
+        for (int idx = tid; idx < PB * (DV / 8); idx += 128) {
+            const int r = idx / (DV / 8), c = (idx - r * (DV / 8)) * 8;
+            const bool ok = b * PB + r <= last_pos && c < vd;
+            cp_async16(dst + r * LV + c, ok ? (const void*)(vp + (size_t)r * G * vd + c) : (const void*)p.v_pool, ok ? 16 : 0);
+        }
+        cp_commit();
+    };
+    auto scores = [&](int b, float (&s)[PB / 8][4]) {
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
-            const int pos = my_pos[half];
-            const bool any = pos >= 0 && b >= my_first[half] / PB && b <= pos / PB;
-            const float* src = my_s[half] + (ptrdiff_t)(b - my_first[half] / PB) * PB + 2 * t;
+            const int pos = my_pos[half], first = my_first[half];
+            const bool any = pos >= 0 && b >= first / PB && b <= pos / PB;
+            const float* src = my_s[half] + (ptrdiff_t)(b - first / PB) * PB;
 #pragma unroll
             for (int nt = 0; nt < PB / 8; ++nt) {
                 float2 v = make_float2(-INFINITY, -INFINITY);
                 if (any) {
                     v = *(const float2*)(src + nt * 8);
                     const int j = b * PB + nt * 8 + 2 * t;
-                    if (j > pos || j < my_first[half]) v.x = -INFINITY;
-                    if (j + 1 > pos || j + 1 < my_first[half]) v.y = -INFINITY;
+                    if (j > pos || j < first) v.x = -INFINITY;
+                    if (j + 1 > pos || j + 1 < first) v.y = -INFINITY;
                 }
                 s[nt][2 * half] = v.x;
                 s[nt][2 * half + 1] = v.y;
             }
         }
-        __syncthreads();                                            // the block before is done with svt
-        const bf16* vp = p.v_pool + ((size_t)page * PB * G + kvh) * vd;
-        for (int idx = tid; idx < PB * (DV / 8); idx += 128) {
-            const int r = idx % PB, c = (idx / PB) * 8;             // consecutive threads, consecutive keys: the 2-byte stores spread over the banks
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (b * PB + r <= last_pos && c < vd) v = *(const uint4*)(vp + (size_t)r * G * vd + c);
-            const bf16* e = (const bf16*)&v;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) svt[(c + i) * (PB + PAD) + r] = e[i];
+    };
+
+    float s[PB / 8][4], s_next[PB / 8][4];
+    stage(b_lo, 0);
+    scores(b_lo, s);
+    for (int b = b_lo; b <= b_hi; ++b) {
+        const int buf = (b - b_lo) & 1;
+        const bool more = b < b_hi;
+        if (more) {
+            stage(b + 1, buf ^ 1);
+            scores(b + 1, s_next);
+            cp_wait<1>();
+        } else {
+            cp_wait<0>();
         }
         __syncthreads();
-        float m_new[2] = {m_run[0], m_run[1]};
+        if (w_any && b >= w_lo && b <= w_hi) {
+            float m_new[2] = {m_run[0], m_run[1]};
 #pragma unroll
-        for (int nt = 0; nt < PB / 8; ++nt)
+            for (int nt = 0; nt < PB / 8; ++nt)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) m_new[e >> 1] = fmaxf(m_new[e >> 1], s[nt][e]);
-        float corr[2];
+                for (int e = 0; e < 4; ++e) m_new[e >> 1] = fmaxf(m_new[e >> 1], s[nt][e]);
+            float corr[2];
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-            m_new[half] = fmaxf(m_new[half], __shfl_xor_sync(0xffffffffu, m_new[half], 1));
-            m_new[half] = fmaxf(m_new[half], __shfl_xor_sync(0xffffffffu, m_new[half], 2));
-            corr[half] = m_new[half] == -INFINITY ? 1.f : expf(m_run[half] - m_new[half]);
-            m_run[half] = m_new[half];
-            l_run[half] *= corr[half];
-        }
+            for (int half = 0; half < 2; ++half) {
+                m_new[half] = fmaxf(m_new[half], __shfl_xor_sync(0xffffffffu, m_new[half], 1));
+                m_new[half] = fmaxf(m_new[half], __shfl_xor_sync(0xffffffffu, m_new[half], 2));
+                corr[half] = m_new[half] == -INFINITY ? 1.f : expf(m_run[half] - m_new[half]);
+                m_run[half] = m_new[half];
+                l_run[half] *= corr[half];
+            }
 #pragma unroll
-        for (int i = 0; i < DV / 8; ++i) {
-            o[i][0] *= corr[0];
-            o[i][1] *= corr[0];
-            o[i][2] *= corr[1];
-            o[i][3] *= corr[1];
-        }
+            for (int i = 0; i < DV / 8; ++i) {
+                o[i][0] *= corr[0];
+                o[i][1] *= corr[0];
+                o[i][2] *= corr[1];
+                o[i][3] *= corr[1];
+            }
 #pragma unroll
-        for (int nt = 0; nt < PB / 8; ++nt) {
+            for (int nt = 0; nt < PB / 8; ++nt) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int half = e >> 1;
-                const float w = m_new[half] == -INFINITY ? 0.f : expf(s[nt][e] - m_new[half]);
-                s[nt][e] = w;
-                l_run[half] += w;
+                for (int e = 0; e < 4; ++e) {
+                    const int half = e >> 1;
+                    const float w = m_new[half] == -INFINITY ? 0.f : expf(s[nt][e] - m_new[half]);
+                    s[nt][e] = w;
+                    l_run[half] += w;
+                }
+            }
+            const bf16* vb = sv + (size_t)buf * PB * LV + (size_t)((lane & 7) + ((lane >> 3) & 1) * 8) * LV + (lane >> 4) * 8;
+#pragma unroll
+            for (int kk = 0; kk < PB / 16; ++kk) {
+                uint32_t hi[4], lw[4];
+                split_bf16(s[2 * kk][0], s[2 * kk][1], hi[0], lw[0]);
+                split_bf16(s[2 * kk][2], s[2 * kk][3], hi[1], lw[1]);
+                split_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1], hi[2], lw[2]);
+                split_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3], hi[3], lw[3]);
+#pragma unroll
+                for (int n2 = 0; n2 < DV / 16; ++n2) {
+                    uint32_t vf[4];                                  // (keys 0-7, 8-15) x (channels n2 * 16, + 8)
+                    ldsm4_trans(vf, vb + (size_t)kk * 16 * LV + n2 * 16);
+                    mma_bf16(o[2 * n2], hi, vf[0], vf[1]);
+                    mma_bf16(o[2 * n2], lw, vf[0], vf[1]);
+                    mma_bf16(o[2 * n2 + 1], hi, vf[2], vf[3]);
+                    mma_bf16(o[2 * n2 + 1], lw, vf[2], vf[3]);
+                }
             }
         }
+        __syncthreads();                                            // the buffer is free for the block after next
+        if (more) {
 #pragma unroll
-        for (int kk = 0; kk < PB / 16; ++kk) {
-            uint32_t hi[4], lw[4];
-            split_bf16(s[2 * kk][0], s[2 * kk][1], hi[0], lw[0]);
-            split_bf16(s[2 * kk][2], s[2 * kk][3], hi[1], lw[1]);
-            split_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1], hi[2], lw[2]);
-            split_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3], hi[3], lw[3]);
+            for (int nt = 0; nt < PB / 8; ++nt)
 #pragma unroll
-            for (int nt = 0; nt < DV / 8; ++nt) {
-                const bf16* vb = svt + (nt * 8 + g) * (PB + PAD) + kk * 16 + 2 * t;
-                const uint32_t b0 = *(const uint32_t*)vb, b1 = *(const uint32_t*)(vb + 8);
-                mma_bf16(o[nt], hi, b0, b1);
-                mma_bf16(o[nt], lw, b0, b1);
-            }
+                for (int e = 0; e < 4; ++e) s[nt][e] = s_next[nt][e];
         }
     }
 #pragma unroll
@@ -686,7 +733,7 @@ __global__ void __launch_bounds__(128, 2) talk_prompt_values_kernel(PromptArgs p
 
 template <int DV>
 int launch_values(const PromptArgs& p, int n_seqs, int max_q_len, cudaStream_t stream) {
-    const size_t smem = (size_t)DV * (PB + 8) * sizeof(bf16);
+    const size_t smem = (size_t)2 * PB * (DV + 8) * sizeof(bf16);
     FR_CUDA(cudaFuncSetAttribute(talk_prompt_values_kernel<DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const dim3 grid((unsigned)((max_q_len + 63) / 64), (unsigned)p.heads, (unsigned)n_seqs);
     FR_CUDA(fr_launch(talk_prompt_values_kernel<DV>, grid, dim3(128), smem, stream, p));
@@ -694,10 +741,29 @@ int launch_values(const PromptArgs& p, int n_seqs, int max_q_len, cudaStream_t s
     return FR_OK;
 }
 
+// elements per staged query row: all heads' channels and a pad that sets neighbouring rows 64 bytes apart modulo 128, so
+// that the eight 16-byte reads of a quarter warp (two rows, four pieces each) meet no bank twice
+int staged_row(int heads, int dim) {
+    const int n = heads * dim;
+    return n + ((32 - n % 64) + 64) % 64;
+}
+
+int padded_heads(int heads) { return heads <= 8 ? 8 : heads <= 16 ? 16 : heads <= 32 ? 32 : 0; }
+
 size_t prompt_scores_smem(int heads, int dim) {
-    const int dkp = (dim + 15) / 16 * 16, h4 = (heads + 3) & ~3;
-    return ((size_t)heads * QR * RAW_LD + (size_t)heads * h4) * sizeof(float) +
-           ((size_t)QR * (heads * dkp + 8) + (size_t)4 * 16 * (dkp + 8)) * sizeof(bf16);
+    const int hp = padded_heads(heads);
+    return ((size_t)hp * hp + hp) * sizeof(float) + (size_t)QR * staged_row(heads, dim) * sizeof(bf16);
+}
+
+template <int HP>
+int launch_scores(const PromptArgs& p, int n_seqs, int max_q_len, cudaStream_t stream) {
+    const size_t smem = prompt_scores_smem(p.heads, p.dim);
+    FR_CUDA(cudaFuncSetAttribute(talk_prompt_scores_kernel<HP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    // a tile of 16 rows sees at most one block more than a single row does
+    const dim3 grid((unsigned)(p.stride / PB + 1), (unsigned)((max_q_len + QR - 1) / QR), (unsigned)n_seqs);
+    FR_CUDA(fr_launch(talk_prompt_scores_kernel<HP>, grid, dim3(256), smem, stream, p));
+    FR_CHECK_LAUNCH("talk prompt scores");
+    return FR_OK;
 }
 
 }  // namespace
@@ -705,7 +771,7 @@ size_t prompt_scores_smem(int heads, int dim) {
 // Floats of scratch memory for the mixed scores of n_rows rows; 0 if the tensor-core kernels do not take these sizes
 // (key channels in eights, value channels in eights up to 128, what the score kernel holds in shared memory).
 FR_EXPORT long long attention_talk_prompt_scratch_floats(int n_rows, int heads, int dim, int vdim, int window, int max_kv_len) {
-    if (heads <= 0 || dim <= 0 || dim % 8 || vdim <= 0 || vdim % 8 || vdim > 128 || heads > 65535) return 0;
+    if (heads <= 0 || padded_heads(heads) == 0 || dim <= 0 || dim % 8 || vdim <= 0 || vdim % 8 || vdim > 128) return 0;
     if (prompt_scores_smem(heads, dim) > 200 * 1024) return 0;
     return (long long)n_rows * heads * prompt_stride(window, max_kv_len);
 }
@@ -728,13 +794,13 @@ FR_EXPORT int attention_talk_prompt(const void* q, int q_ld, const void* k_pool,
     PromptArgs p;
     p.q = (const bf16*)q; p.q_ld = q_ld; p.k_pool = (const bf16*)k_pool; p.v_pool = (const bf16*)v_pool; p.table = table;
     p.table_width = table_width; p.seq_start = seq_start; p.seq_qlen = seq_qlen; p.seq_pos0 = seq_pos0; p.heads = heads;
-    p.kv_heads = kv_heads; p.dim = dim; p.dkp = (dim + 15) / 16 * 16; p.vdim = vdim; p.window = window;
+    p.kv_heads = kv_heads; p.dim = dim; p.q_ld_s = staged_row(heads, dim); p.vdim = vdim; p.window = window;
     p.stride = prompt_stride(window, max_kv_len); p.scale = scale; p.slopes = slopes; p.talk = FrVec{talk, talk_dtype};
     p.gate = (const bf16*)gate; p.gate_ld = gate_ld; p.out = (bf16*)out; p.mixed = scratch;
-    const size_t smem = prompt_scores_smem(heads, dim);
-    FR_CUDA(cudaFuncSetAttribute(talk_prompt_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    FR_CUDA(fr_launch(talk_prompt_scores_kernel, dim3((unsigned)((max_q_len + QR - 1) / QR), (unsigned)n_seqs), dim3(128), smem, stream, p));
-    FR_CHECK_LAUNCH("talk prompt scores");
+    const int hp = padded_heads(heads);
+    const int rc = hp == 8 ? launch_scores<8>(p, n_seqs, max_q_len, stream)
+                 : hp == 16 ? launch_scores<16>(p, n_seqs, max_q_len, stream) : launch_scores<32>(p, n_seqs, max_q_len, stream);
+    if (rc != FR_OK) return rc;
     if (vdim <= 32) return launch_values<32>(p, n_seqs, max_q_len, stream);
     if (vdim <= 64) return launch_values<64>(p, n_seqs, max_q_len, stream);
     return launch_values<128>(p, n_seqs, max_q_len, stream);
