@@ -386,6 +386,7 @@ FR_EXPORT int attention_talk_rows(const void* q, int q_ld, const void* k_pool, c
 namespace {
 
 constexpr int PB = 64;             // keys per block: a page of the cache
+constexpr float LOG2E = 1.4426950408889634f;
 constexpr int QR = 16;             // rows of a sequence per CTA of the score kernel
 
 static int prompt_stride(int window, int max_kv_len) {
@@ -395,7 +396,7 @@ static int prompt_stride(int window, int max_kv_len) {
 }
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
@@ -485,13 +486,18 @@ __global__ void __launch_bounds__(256) talk_prompt_scores_kernel(PromptArgs p) {
         const int ch = c * 32 + t4 * 8;                             // this thread's eight channels of the group
         const bool ch_ok = ch < dim;
         uint4 kf = make_uint4(0, 0, 0, 0);
+        int left = 0;                                               // heads that still use the key head in kf
+        const bf16* kg = krow + ch;
 #pragma unroll
         for (int h = 0; h < HP; ++h) {
             if (h < H) {
-                if (h % per == 0) {
+                if (left == 0) {
                     kf = make_uint4(0, 0, 0, 0);
-                    if (key_ok && ch_ok) kf = *(const uint4*)(krow + (size_t)(h / per) * dim + ch);
+                    if (key_ok && ch_ok) kf = *(const uint4*)kg;
+                    kg += dim;
+                    left = per;
                 }
+                --left;
                 uint4 qa = make_uint4(0, 0, 0, 0), qb = qa;
                 if (ch_ok) {
                     qa = *(const uint4*)(qa_row + (size_t)h * dim + c * 32);
@@ -615,18 +621,21 @@ __global__ void __launch_bounds__(128, 2) talk_prompt_values_kernel(PromptArgs p
         for (int half = 0; half < 2; ++half) {
             const int pos = my_pos[half], first = my_first[half];
             const bool any = pos >= 0 && b >= first / PB && b <= pos / PB;
+            const bool whole = b * PB >= first && b * PB + PB - 1 <= pos;          // the row sees every key of the block
             const float* src = my_s[half] + (ptrdiff_t)(b - first / PB) * PB;
 #pragma unroll
             for (int nt = 0; nt < PB / 8; ++nt) {
                 float2 v = make_float2(-INFINITY, -INFINITY);
                 if (any) {
                     v = *(const float2*)(src + nt * 8);
-                    const int j = b * PB + nt * 8 + 2 * t;
-                    if (j > pos || j < first) v.x = -INFINITY;
-                    if (j + 1 > pos || j + 1 < first) v.y = -INFINITY;
+                    if (!whole) {
+                        const int j = b * PB + nt * 8 + 2 * t;
+                        if (j > pos || j < first) v.x = -INFINITY;
+                        if (j + 1 > pos || j + 1 < first) v.y = -INFINITY;
+                    }
                 }
-                s[nt][2 * half] = v.x;
-                s[nt][2 * half + 1] = v.y;
+                s[nt][2 * half] = v.x * LOG2E;                      // the softmax runs on powers of two
+                s[nt][2 * half + 1] = v.y * LOG2E;
             }
         }
     };
@@ -656,7 +665,7 @@ __global__ void __launch_bounds__(128, 2) talk_prompt_values_kernel(PromptArgs p
             for (int half = 0; half < 2; ++half) {
                 m_new[half] = fmaxf(m_new[half], __shfl_xor_sync(0xffffffffu, m_new[half], 1));
                 m_new[half] = fmaxf(m_new[half], __shfl_xor_sync(0xffffffffu, m_new[half], 2));
-                corr[half] = m_new[half] == -INFINITY ? 1.f : expf(m_run[half] - m_new[half]);
+                corr[half] = m_new[half] == -INFINITY ? 1.f : exp2f(m_run[half] - m_new[half]);
                 m_run[half] = m_new[half];
                 l_run[half] *= corr[half];
             }
@@ -672,7 +681,7 @@ __global__ void __launch_bounds__(128, 2) talk_prompt_values_kernel(PromptArgs p
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int half = e >> 1;
-                    const float w = m_new[half] == -INFINITY ? 0.f : expf(s[nt][e] - m_new[half]);
+                    const float w = m_new[half] == -INFINITY ? 0.f : exp2f(s[nt][e] - m_new[half]);
                     s[nt][e] = w;
                     l_run[half] += w;
                 }
@@ -690,8 +699,8 @@ __global__ void __launch_bounds__(128, 2) talk_prompt_values_kernel(PromptArgs p
                     uint32_t vf[4];                                  // (keys 0-7, 8-15) x (channels n2 * 16, + 8)
                     ldsm4_trans(vf, vb + (size_t)kk * 16 * LV + n2 * 16);
                     mma_bf16(o[2 * n2], hi, vf[0], vf[1]);
-                    mma_bf16(o[2 * n2], lw, vf[0], vf[1]);
                     mma_bf16(o[2 * n2 + 1], hi, vf[2], vf[3]);
+                    mma_bf16(o[2 * n2], lw, vf[0], vf[1]);
                     mma_bf16(o[2 * n2 + 1], lw, vf[2], vf[3]);
                 }
             }
