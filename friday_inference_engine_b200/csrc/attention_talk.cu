@@ -33,6 +33,15 @@ namespace {
 
 constexpr int KS = 64;             // keys per block of the CUDA-core kernel
 constexpr int HC = 4;              // heads whose weighted values a thread sums at a time
+constexpr int KS_MIN = 16;         // fewest keys per block of the staged kernel
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, int src_bytes) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // ------------------------------------------------------------------ store
 template <typename T>
@@ -75,6 +84,7 @@ struct SplitArgs {
     const int* row_seq;
     const int* row_pos;
     int heads, kv_heads, dim, vdim, window, splits;
+    int ks;                     // keys per block
     float scale;
     const float* slopes;        // [heads] or null
     FrVec talk;                 // [heads][heads] or null
@@ -257,46 +267,229 @@ __global__ void __launch_bounds__(128) talk_split_kernel(SplitArgs p) {
     }
 }
 
+__device__ __forceinline__ void load_pair(const float* p, float& a, float& b) {
+    const float2 v = *(const float2*)p;
+    a = v.x; b = v.y;
+}
+__device__ __forceinline__ void load_pair(const bf16* p, float& a, float& b) {
+    const uint32_t v = *(const uint32_t*)p;
+    a = __uint_as_float(v << 16); b = __uint_as_float(v & 0xffff0000u);
+}
+
+// The same block of work with the keys and values of its `ks` keys (a multiple of four, at most KS) brought into shared
+// memory first: every thread issues its 16-byte copies at once, so the block's whole share of the cache is in flight
+// together, and queries and the mixing matrix are read meanwhile.  256 threads: four lanes per key for the scores, a
+// thread per pair of value channels of a key head for the weighted values.  A key's row in shared memory is 64 bytes
+// longer than its channels, so that the 16-byte reads of two neighbouring keys fall on different banks.
+template <typename T>
+__global__ void __launch_bounds__(256) talk_staged_kernel(SplitArgs p) {
+    constexpr int VEC = 16 / (int)sizeof(T);
+    extern __shared__ __align__(16) float sm[];
+    const int H = p.heads, G = p.kv_heads, dim = p.dim, vd = p.vdim, per = H / G, ks = p.ks;
+    const int krow_len = G * dim + 64 / (int)sizeof(T), vrow_len = G * vd;
+    float* ms = sm;                                     // [H][ks] mixed scores, then weights
+    float* ss = ms + (size_t)H * ks;                    // [H][ks] raw scores
+    float* qs = ss + (size_t)H * ks;                    // [H][dim]
+    float* tk = qs + (size_t)H * dim;                   // [H][H]
+    float* stat = tk + (size_t)H * H;                   // [H][2]
+    T* kt = (T*)(((uintptr_t)(stat + 2 * (size_t)H) + 15) & ~(uintptr_t)15);   // [ks][krow_len], 16-byte aligned
+    T* vt = kt + (size_t)ks * krow_len;                 // [ks][vrow_len]
+    const int row = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int seq = p.row_seq[row];
+    fr_pdl_wait();
+    fr_pdl_launch();
+    if (seq < 0) return;
+    const int pos = p.row_pos[row];
+    const int j0 = max(0, pos - p.window + 1), n = pos - j0 + 1;
+    const int t0 = blockIdx.x * ks;
+    if (t0 >= n) return;
+    const int kn = min(ks, n - t0);
+    const int* tab = p.table + (size_t)seq * p.table_width;
+    {
+        const T* kp = (const T*)p.k_pool;
+        const T* vp = (const T*)p.v_pool;
+        const int kc = G * dim / VEC, vc = G * vd / VEC;            // 16-byte pieces of a key's and of a value's row
+        for (int i = tid; i < ks * (kc + vc); i += 256) {
+            const int t = i / (kc + vc), c = i - t * (kc + vc);
+            const int j = j0 + t0 + min(t, kn - 1);                  // slots past the row's last key repeat it; their weights are 0
+            const size_t at = (size_t)tab[j / p.page] * p.page + j % p.page;
+            if (c < kc) cp_async16(kt + (size_t)t * krow_len + c * VEC, kp + at * G * dim + c * VEC, 16);
+            else cp_async16(vt + (size_t)t * vrow_len + (c - kc) * VEC, vp + at * G * vd + (c - kc) * VEC, 16);
+        }
+        cp_commit();
+    }
+    const T* q = (const T*)p.q + (size_t)row * p.q_ld;
+    for (int i = tid; i < H * dim; i += 256) qs[i] = fr_load(q + i);
+    if (p.talk.p != nullptr)
+        for (int i = tid; i < H * H; i += 256) tk[i] = p.talk.at(i);
+    cp_wait<0>();
+    __syncthreads();
+    const int c4 = tid & 3, nchunks = dim / VEC;
+    for (int t = tid >> 2; t < ks; t += 64) {
+        const float dist = (float)(pos - (j0 + t0 + t));
+        const T* krow = kt + (size_t)t * krow_len;
+        for (int g = 0; g < G; ++g) {
+            for (int hc = 0; hc < per; hc += 8) {
+                float acc[8];
+#pragma unroll
+                for (int a = 0; a < 8; ++a) acc[a] = 0.f;
+                for (int ci = c4; ci < nchunks; ci += 4) {
+                    float kf[VEC];
+                    Chunk<T, VEC>::load(krow + (size_t)g * dim + ci * VEC, kf);
+#pragma unroll
+                    for (int a = 0; a < 8; ++a) {
+                        if (hc + a < per) {
+                            const float* qh = qs + (size_t)(g * per + hc + a) * dim + ci * VEC;
+                            float s = acc[a];
+#pragma unroll
+                            for (int e = 0; e < VEC / 4; ++e) {
+                                const float4 qv = *(const float4*)(qh + 4 * e);
+                                s = fmaf(qv.x, kf[4 * e], fmaf(qv.y, kf[4 * e + 1], fmaf(qv.z, kf[4 * e + 2], fmaf(qv.w, kf[4 * e + 3], s))));
+                            }
+                            acc[a] = s;
+                        }
+                    }
+                }
+#pragma unroll
+                for (int a = 0; a < 8; ++a) {
+                    if (hc + a < per) {
+                        float s = acc[a];
+                        s += __shfl_xor_sync(0xffffffffu, s, 1);
+                        s += __shfl_xor_sync(0xffffffffu, s, 2);
+                        if (c4 == 0) {
+                            const int h = g * per + hc + a;
+                            s *= p.scale;
+                            if (p.slopes != nullptr) s -= p.slopes[h] * dist;
+                            ss[h * ks + t] = s;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < H * ks; idx += 256) {
+        const int h = idx / ks, t = idx - h * ks;
+        float s;
+        if (p.talk.p != nullptr) {
+            s = 0.f;
+            for (int g = 0; g < H; ++g) s = fmaf(tk[h * H + g], ss[g * ks + t], s);
+        } else {
+            s = ss[idx];
+        }
+        ms[idx] = t < kn ? s : -INFINITY;
+    }
+    __syncthreads();
+    for (int h = warp; h < H; h += 8) {
+        float* s = ms + (size_t)h * ks;
+        float m = -INFINITY;
+        for (int t = lane; t < ks; t += 32) m = fmaxf(m, s[t]);
+        m = fr_warp_max(m);
+        float sum = 0.f;
+        for (int t = lane; t < ks; t += 32) {
+            const float w = expf(s[t] - m);            // slots past the row's last key: exp(-inf) = 0
+            s[t] = w;
+            sum += w;
+        }
+        sum = fr_warp_sum(sum);
+        if (lane == 0) {
+            stat[2 * h] = m;
+            stat[2 * h + 1] = sum;
+        }
+    }
+    __syncthreads();
+    float* part = p.part + ((size_t)row * p.splits + blockIdx.x) * H * (vd + 2);
+    const int half = vd / 2;
+    for (int item = tid; item < G * half; item += 256) {
+        const int g = item / half, d = 2 * (item - g * half);
+        const T* vcol = vt + (size_t)g * vd + d;
+        for (int hc = 0; hc < per; hc += HC) {
+            float a0[HC], a1[HC];
+#pragma unroll
+            for (int a = 0; a < HC; ++a) a0[a] = a1[a] = 0.f;
+            for (int t = 0; t < ks; t += 4) {
+                float x[4], y[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) load_pair(vcol + (size_t)(t + e) * vrow_len, x[e], y[e]);
+#pragma unroll
+                for (int a = 0; a < HC; ++a) {
+                    if (hc + a < per) {
+                        const float4 w = *(const float4*)(ms + (size_t)(g * per + hc + a) * ks + t);
+                        a0[a] = fmaf(w.x, x[0], fmaf(w.y, x[1], fmaf(w.z, x[2], fmaf(w.w, x[3], a0[a]))));
+                        a1[a] = fmaf(w.x, y[0], fmaf(w.y, y[1], fmaf(w.z, y[2], fmaf(w.w, y[3], a1[a]))));
+                    }
+                }
+            }
+#pragma unroll
+            for (int a = 0; a < HC; ++a)
+                if (hc + a < per) *(float2*)(part + (size_t)(g * per + hc + a) * (vd + 2) + d) = make_float2(a0[a], a1[a]);
+        }
+    }
+    for (int h = tid; h < H; h += 256) {
+        part[(size_t)h * (vd + 2) + vd] = stat[2 * h];
+        part[(size_t)h * (vd + 2) + vd + 1] = stat[2 * h + 1];
+    }
+}
+
 struct MergeTalkArgs {
     const float* part;          // [rows][splits][heads][vdim + 2]
     const int* row_seq;
     const int* row_pos;
-    int heads, vdim, window, splits;
+    int heads, vdim, window, splits, ks;
     const void* gate;           // [rows][gate_ld], head h's gates at h * vdim; or null
     int gate_ld;
     void* out;                  // [rows][heads * vdim]
 };
 
-// out_h = sum_s o_s exp(m_s - M) / sum_s l_s exp(m_s - M) over the row's blocks of keys, times sigmoid(gate) if given
+// out_h = sum_s o_s exp(m_s - M) / sum_s l_s exp(m_s - M) over the row's blocks of keys, times sigmoid(gate) if given.
+// A block per (head, row): the blocks' factors are found once, in shared memory, then a thread per value channel sums.
 template <typename T>
 __global__ void __launch_bounds__(128) talk_merge_kernel(MergeTalkArgs p) {
-    const int row = blockIdx.x, H = p.heads, vd = p.vdim;
+    extern __shared__ __align__(16) float sm[];            // [splits] factors
+    __shared__ float red[8];
+    const int h = blockIdx.x, row = blockIdx.y, H = p.heads, vd = p.vdim, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int seq = p.row_seq[row];
     fr_pdl_wait();
     fr_pdl_launch();
     if (seq < 0) return;
     const int pos = p.row_pos[row];
     const int n = pos - max(0, pos - p.window + 1) + 1;
-    const int ns = (n + KS - 1) / KS;
-    const float* part = p.part + (size_t)row * p.splits * H * (vd + 2);
+    const int ns = (n + p.ks - 1) / p.ks;
     const size_t step = (size_t)H * (vd + 2);
-    for (int idx = threadIdx.x; idx < H * vd; idx += 128) {
-        const int h = idx / vd, d = idx - h * vd;
-        const float* ph = part + (size_t)h * (vd + 2);
-        float big = -INFINITY;
-        for (int s = 0; s < ns; ++s) big = fmaxf(big, ph[s * step + vd]);
-        float l = 0.f, o = 0.f;
-        for (int s = 0; s < ns; ++s) {
-            const float f = expf(ph[s * step + vd] - big);
-            l = fmaf(ph[s * step + vd + 1], f, l);
-            o = fmaf(ph[s * step + d], f, o);
+    const float* ph = p.part + (size_t)row * p.splits * step + (size_t)h * (vd + 2);
+    float big = -INFINITY;
+    for (int s = tid; s < ns; s += 128) big = fmaxf(big, ph[s * step + vd]);
+    big = fr_warp_max(big);
+    if (lane == 0) red[warp] = big;
+    __syncthreads();
+    big = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    float l = 0.f;
+    for (int s = tid; s < ns; s += 128) {
+        const float f = expf(ph[s * step + vd] - big);
+        sm[s] = f;
+        l = fmaf(ph[s * step + vd + 1], f, l);
+    }
+    l = fr_warp_sum(l);
+    if (lane == 0) red[4 + warp] = l;
+    __syncthreads();
+    l = (red[4] + red[5]) + (red[6] + red[7]);
+    const float inv = 1.0f / l;
+    for (int d = tid; d < vd; d += 128) {
+        float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+        int s = 0;
+        for (; s + 4 <= ns; s += 4) {
+            o0 = fmaf(ph[s * step + d], sm[s], o0);
+            o1 = fmaf(ph[(s + 1) * step + d], sm[s + 1], o1);
+            o2 = fmaf(ph[(s + 2) * step + d], sm[s + 2], o2);
+            o3 = fmaf(ph[(s + 3) * step + d], sm[s + 3], o3);
         }
-        o /= l;
+        for (; s < ns; ++s) o0 = fmaf(ph[s * step + d], sm[s], o0);
+        float o = ((o0 + o1) + (o2 + o3)) * inv;
         if (p.gate != nullptr) {
-            const float g = fr_load((const T*)p.gate + (size_t)row * p.gate_ld + idx);
+            const float g = fr_load((const T*)p.gate + (size_t)row * p.gate_ld + (size_t)h * vd + d);
             o *= 1.0f / (1.0f + expf(-g));
         }
-        fr_store((T*)p.out + (size_t)row * H * vd + idx, o);
+        fr_store((T*)p.out + (size_t)row * H * vd + (size_t)h * vd + d, o);
     }
 }
 
@@ -327,14 +520,15 @@ FR_EXPORT int attention_talk_store(void* src, int ld, int k_off, int v_off, int 
     return FR_OK;
 }
 
-// Floats of scratch memory that `attention_talk_rows` needs for n_rows rows: what every block of KS keys of a row leaves.
-static int talk_splits(int window, int max_kv_len) {
+// Floats of scratch memory that `attention_talk_rows` needs for n_rows rows: what every block of keys of a row leaves, sized
+// for the smallest blocks.
+static int talk_span(int window, int max_kv_len) {
     const int span = window > 0 && window < max_kv_len ? window : max_kv_len;
-    return span > 0 ? (span + KS - 1) / KS : 1;
+    return span > 0 ? span : 1;
 }
 
 FR_EXPORT long long attention_talk_scratch_floats(int n_rows, int heads, int vdim, int window, int max_kv_len) {
-    return (long long)n_rows * talk_splits(window, max_kv_len) * heads * (vdim + 2);
+    return (long long)n_rows * ((talk_span(window, max_kv_len) + KS_MIN - 1) / KS_MIN) * heads * (vdim + 2);
 }
 
 template <typename T, int VEC>
@@ -344,8 +538,24 @@ static cudaError_t launch_split(const SplitArgs& p, dim3 grid, size_t smem, cuda
     return fr_launch(talk_split_kernel<T, VEC>, grid, dim3(128), smem, stream, p);
 }
 
+template <typename T>
+static cudaError_t launch_staged(const SplitArgs& p, dim3 grid, size_t smem, cudaStream_t stream) {
+    cudaError_t e = cudaFuncSetAttribute(talk_staged_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    return fr_launch(talk_staged_kernel<T>, grid, dim3(256), smem, stream, p);
+}
+
+// shared memory of the staged kernel with ks keys per block
+static size_t staged_bytes(int ks, int heads, int kv_heads, int dim, int vdim, size_t esz) {
+    return (2 * (size_t)heads * ks + (size_t)heads * dim + (size_t)heads * heads + 2 * (size_t)heads) * sizeof(float) + 16 +
+           (size_t)ks * ((size_t)kv_heads * dim * esz + 64) + (size_t)ks * kv_heads * vdim * esz;
+}
+
 // out [n_rows][heads * vdim]: every row's attention over the keys of its window, on the CUDA cores, in two launches: blocks of
-// KS keys, then their merge (with the gate).  q: [n_rows][q_ld], head h at h * dim; gate (or null): [n_rows][gate_ld].
+// keys, then their merge (with the gate).  q: [n_rows][q_ld], head h at h * dim; gate (or null): [n_rows][gate_ld].
+// Where rows of keys and values are whole 16-byte pieces the blocks stage them in shared memory, with as many keys per
+// block (64, 32 or 16) as fit there and leave about one and a half blocks per SM or more; otherwise blocks of 64 keys read
+// them from the cache as they go.
 FR_EXPORT int attention_talk_rows(const void* q, int q_ld, const void* k_pool, const void* v_pool, const int* table, int table_width,
                                   int page, const int* row_seq, const int* row_pos, int n_rows, int heads, int kv_heads, int dim, int vdim,
                                   int window, int max_kv_len, float scale, const float* slopes, const void* talk, int talk_dtype,
@@ -355,26 +565,49 @@ FR_EXPORT int attention_talk_rows(const void* q, int q_ld, const void* k_pool, c
         FR_REFUSE("talk attention: %d heads on %d key heads of %d and %d", heads, kv_heads, dim, vdim);
     if (dtype != FR_F32 && dtype != FR_BF16) FR_REFUSE("talk attention: unknown dtype %d", dtype);
     if (window <= 0) window = max_kv_len;
+    const int span = talk_span(window, max_kv_len);
     SplitArgs p;
     p.q = q; p.q_ld = q_ld; p.k_pool = k_pool; p.v_pool = v_pool; p.table = table; p.table_width = table_width; p.page = page;
     p.row_seq = row_seq; p.row_pos = row_pos; p.heads = heads; p.kv_heads = kv_heads; p.dim = dim; p.vdim = vdim; p.window = window;
-    p.splits = talk_splits(window, max_kv_len);
     p.scale = scale; p.slopes = slopes; p.talk = FrVec{talk, talk_dtype}; p.part = scratch;
-    const size_t smem = ((size_t)KS + 2 * (size_t)heads * KS + (size_t)heads * dim + (size_t)heads * heads + 2 * (size_t)heads) * sizeof(float);
-    if (smem > 200 * 1024) FR_REFUSE("talk attention: %d heads of %d need %zu bytes of shared memory", heads, dim, smem);
-    const dim3 grid((unsigned)p.splits, (unsigned)n_rows);
     const size_t esz = dtype == FR_F32 ? 4 : 2;
-    const bool aligned = ((uintptr_t)k_pool % 16) == 0 && ((size_t)dim * esz) % 16 == 0;
+    const bool k_pieces = ((uintptr_t)k_pool % 16) == 0 && ((size_t)dim * esz) % 16 == 0;
+    const bool v_pieces = ((uintptr_t)v_pool % 16) == 0 && ((size_t)vdim * esz) % 16 == 0 && ((uintptr_t)scratch % 8) == 0;
+    const size_t room = 200 * 1024;
+    int ks = 0;
+    if (k_pieces && v_pieces) {
+        ks = KS;
+        while (ks > KS_MIN && (staged_bytes(ks, heads, kv_heads, dim, vdim, esz) > room ||
+                               (long long)n_rows * ((span + ks - 1) / ks) < 222))
+            ks /= 2;
+        if (staged_bytes(ks, heads, kv_heads, dim, vdim, esz) > room) ks = 0;
+    }
     cudaError_t launched;
-    if (dtype == FR_F32) launched = aligned ? launch_split<float, 4>(p, grid, smem, stream) : launch_split<float, 1>(p, grid, smem, stream);
-    else launched = aligned ? launch_split<bf16, 8>(p, grid, smem, stream) : launch_split<bf16, 1>(p, grid, smem, stream);
+    if (ks > 0) {
+        p.ks = ks;
+        p.splits = (span + ks - 1) / ks;
+        const dim3 grid((unsigned)p.splits, (unsigned)n_rows);
+        const size_t smem = staged_bytes(ks, heads, kv_heads, dim, vdim, esz);
+        launched = dtype == FR_F32 ? launch_staged<float>(p, grid, smem, stream) : launch_staged<bf16>(p, grid, smem, stream);
+    } else {
+        p.ks = KS;
+        p.splits = (span + KS - 1) / KS;
+        const dim3 grid((unsigned)p.splits, (unsigned)n_rows);
+        const size_t smem = ((size_t)KS + 2 * (size_t)heads * KS + (size_t)heads * dim + (size_t)heads * heads + 2 * (size_t)heads) * sizeof(float);
+        if (smem > room) FR_REFUSE("talk attention: %d heads of %d need %zu bytes of shared memory", heads, dim, smem);
+        if (dtype == FR_F32) launched = k_pieces ? launch_split<float, 4>(p, grid, smem, stream) : launch_split<float, 1>(p, grid, smem, stream);
+        else launched = k_pieces ? launch_split<bf16, 8>(p, grid, smem, stream) : launch_split<bf16, 1>(p, grid, smem, stream);
+    }
     FR_CUDA(launched);
-    FR_CHECK_LAUNCH("talk split");
+    FR_CHECK_LAUNCH("talk blocks");
     MergeTalkArgs m;
     m.part = scratch; m.row_seq = row_seq; m.row_pos = row_pos; m.heads = heads; m.vdim = vdim; m.window = window; m.splits = p.splits;
-    m.gate = gate; m.gate_ld = gate_ld; m.out = out;
-    if (dtype == FR_F32) FR_CUDA(fr_launch(talk_merge_kernel<float>, dim3(n_rows), dim3(128), 0, stream, m));
-    else FR_CUDA(fr_launch(talk_merge_kernel<bf16>, dim3(n_rows), dim3(128), 0, stream, m));
+    m.ks = p.ks; m.gate = gate; m.gate_ld = gate_ld; m.out = out;
+    const dim3 mgrid((unsigned)heads, (unsigned)n_rows);
+    const size_t msm = (size_t)p.splits * sizeof(float);
+    if (msm > 48 * 1024) FR_REFUSE("talk attention: %d blocks of keys per row are more than the merge takes", p.splits);
+    if (dtype == FR_F32) FR_CUDA(fr_launch(talk_merge_kernel<float>, mgrid, dim3(128), msm, stream, m));
+    else FR_CUDA(fr_launch(talk_merge_kernel<bf16>, mgrid, dim3(128), msm, stream, m));
     FR_CHECK_LAUNCH("talk merge");
     return FR_OK;
 }
@@ -557,13 +790,6 @@ __device__ __forceinline__ void ldsm4_trans(uint32_t (&r)[4], const void* p) {
     const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
 }
-__device__ __forceinline__ void cp_async16(void* dst, const void* src, int src_bytes) {
-    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(src_bytes) : "memory");
-}
-__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // 64 rows of a sequence and one head: the softmax of the mixed scores, block of keys by block of keys with a running
 // maximum and sum, and the weights times the values on the tensor cores.  A thread reads the scores of its places of the
