@@ -538,6 +538,149 @@ __global__ void two_sided_act_kernel(T* __restrict__ z, long long n, FrVec pq) {
     }
 }
 
+// ---- the same three row-wise kernels for rows of whole 16-byte pieces that a block can hold in registers (a thread keeps
+// NV pieces of four floats): every input is read once, 16 bytes at a time, and the arithmetic is the scalar kernels'.
+__device__ __forceinline__ void store4(float* p, const float (&v)[4]) { *(float4*)p = make_float4(v[0], v[1], v[2], v[3]); }
+__device__ __forceinline__ void store4(bf16* p, const float (&v)[4]) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    *(uint2*)p = make_uint2(*(const uint32_t*)&a, *(const uint32_t*)&b);
+}
+
+template <typename TO, int NV>
+__global__ void __launch_bounds__(256)
+norm_shift_vec_kernel(const float* __restrict__ x, FrVec w, FrVec shift, TO* __restrict__ y, float* __restrict__ state, long long state_stride,
+                      const int* __restrict__ row_seq, const int* __restrict__ seq_start, const int* __restrict__ seq_slots, int width,
+                      float eps, int save) {
+    __shared__ float partial[32];
+    fr_pdl_wait();
+    fr_pdl_launch();
+    const int row = blockIdx.x;
+    const int seq = row_seq[row];
+    if (seq < 0) return;
+    const bool first = row == seq_start[seq];
+    const float4* xr = (const float4*)(x + (size_t)row * width);
+    const float4* xb = (const float4*)(x + (size_t)row * width - width);
+    float* sp = state + (size_t)seq_slots[seq] * state_stride;
+    const int n4 = width >> 2;
+    float4 a[NV], b[NV];
+    float ss = 0.f, sb = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = threadIdx.x + k * 256;
+        if (i < n4) {
+            a[k] = xr[i];
+            b[k] = first ? ((const float4*)sp)[i] : xb[i];
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = threadIdx.x + k * 256;
+        if (i < n4) {
+            ss = fmaf(a[k].x, a[k].x, ss); ss = fmaf(a[k].y, a[k].y, ss); ss = fmaf(a[k].z, a[k].z, ss); ss = fmaf(a[k].w, a[k].w, ss);
+            if (!first) {
+                sb = fmaf(b[k].x, b[k].x, sb); sb = fmaf(b[k].y, b[k].y, sb); sb = fmaf(b[k].z, b[k].z, sb); sb = fmaf(b[k].w, b[k].w, sb);
+            }
+        }
+    }
+    ss = block_sum(ss, partial);
+    sb = block_sum(sb, partial);
+    const float inv = 1.0f / sqrtf(ss / (float)width + eps), invb = 1.0f / sqrtf(sb / (float)width + eps);
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = threadIdx.x + k * 256;
+        if (i < n4) {
+            const float av[4] = {a[k].x, a[k].y, a[k].z, a[k].w}, bv[4] = {b[k].x, b[k].y, b[k].z, b[k].w};
+            float h[4], o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float wi = w.at(4 * i + e);
+                h[e] = av[e] * inv * wi;
+                const float before = first ? bv[e] : bv[e] * invb * wi;
+                o[e] = fmaf(before - h[e], shift.at(4 * i + e), h[e]);
+            }
+            store4(y + (size_t)row * width + 4 * i, o);
+            if (save) store4(sp + 4 * i, h);
+        }
+    }
+}
+
+template <typename TO, int NV>
+__global__ void __launch_bounds__(256)
+post_norm_add_vec_kernel(const float* __restrict__ x, const float* __restrict__ y, FrVec w, float eps, float mult, float* __restrict__ out,
+                         FrVec w2, float eps2, TO* __restrict__ next, int width) {
+    __shared__ float partial[32];
+    fr_pdl_wait();
+    fr_pdl_launch();
+    const size_t base = (size_t)blockIdx.x * width;
+    const int n4 = width >> 2;
+    float4 v[NV], r[NV];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = threadIdx.x + k * 256;
+        if (i < n4) {
+            v[k] = ((const float4*)(y + base))[i];
+            r[k] = ((const float4*)(x + base))[i];
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = threadIdx.x + k * 256;
+        if (i < n4) { ss = fmaf(v[k].x, v[k].x, ss); ss = fmaf(v[k].y, v[k].y, ss); ss = fmaf(v[k].z, v[k].z, ss); ss = fmaf(v[k].w, v[k].w, ss); }
+    }
+    ss = block_sum(ss, partial);
+    const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+    float s2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = threadIdx.x + k * 256;
+        if (i < n4) {
+            const float yv[4] = {v[k].x, v[k].y, v[k].z, v[k].w}, xv[4] = {r[k].x, r[k].y, r[k].z, r[k].w};
+            float o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                o[e] = fmaf(mult, yv[e] * inv * w.at(4 * i + e), xv[e]);
+                s2 = fmaf(o[e], o[e], s2);
+            }
+            store4(out + base + 4 * i, o);
+            v[k] = make_float4(o[0], o[1], o[2], o[3]);
+        }
+    }
+    if (next == nullptr) return;
+    s2 = block_sum(s2, partial);
+    const float inv2 = 1.0f / sqrtf(s2 / (float)width + eps2);
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = threadIdx.x + k * 256;
+        if (i < n4) {
+            const float ov[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+            float o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[e] = ov[e] * inv2 * w2.at(4 * i + e);
+            store4(next + base + 4 * i, o);
+        }
+    }
+}
+
+// 16 bytes of z per thread and turn
+template <typename T>
+__global__ void two_sided_act_vec_kernel(T* __restrict__ z, long long pieces, FrVec pq) {
+    constexpr int PER = 16 / (int)sizeof(T);
+    fr_pdl_wait();
+    fr_pdl_launch();
+    const float a = softplus_f(pq.at(0)), b = 0.5f + softplus_f(pq.at(1));
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < pieces; i += (long long)gridDim.x * blockDim.x) {
+        uint4 raw = ((const uint4*)z)[i];
+        T* e = (T*)&raw;
+#pragma unroll
+        for (int k = 0; k < PER; ++k) {
+            const float v = fr_load(e + k);
+            fr_store(e + k, v > 0.f ? fmaf(a * v, v, 0.5f * v) : fmaf(b, expm1f(v) - v, 0.5f * v));
+        }
+        ((uint4*)z)[i] = raw;
+    }
+}
+
 }  // namespace
 
 FR_EXPORT int residual_embed_pos(const int* tokens, const int* row_pos, const void* table, const void* positions, int table_dtype, float* out,
@@ -562,7 +705,17 @@ FR_EXPORT int residual_norm_shift(const float* x, const void* w, int w_dtype, co
     if (n_rows <= 0) return FR_OK;
     if (state == nullptr || state_stride < width) FR_REFUSE("norm_shift: a state of at least the width per sequence");
     const FrVec wv{w, w_dtype}, sv{shift, shift_dtype};
-    if (out_dtype == FR_F32)
+    const bool pieces = width % 4 == 0 && width <= 8192 && state_stride % 4 == 0 &&
+                        ((((uintptr_t)x) | ((uintptr_t)y) | ((uintptr_t)state)) & 15) == 0;
+#define SHIFT_VEC(TO, NV)                                                                                                          \
+    FR_CUDA(fr_launch(norm_shift_vec_kernel<TO, NV>, dim3(n_rows), dim3(256), 0, stream, x, wv, sv, (TO*)y, state, state_stride, row_seq, \
+                      seq_start, seq_slots, width, eps, decode ? 1 : 0))
+    if (pieces && out_dtype == FR_F32) {
+        if (width <= 2048) SHIFT_VEC(float, 2); else if (width <= 4096) SHIFT_VEC(float, 4); else SHIFT_VEC(float, 8);
+    } else if (pieces && out_dtype == FR_BF16) {
+        if (width <= 2048) SHIFT_VEC(bf16, 2); else if (width <= 4096) SHIFT_VEC(bf16, 4); else SHIFT_VEC(bf16, 8);
+    } else if (out_dtype == FR_F32)
+#undef SHIFT_VEC
         FR_CUDA(fr_launch(norm_shift_kernel<float>, dim3(n_rows), dim3(256), 0, stream, x, wv, sv, (float*)y, state, state_stride, row_seq,
                           seq_start, seq_slots, width, eps, decode ? 1 : 0));
     else if (out_dtype == FR_BF16)
@@ -583,7 +736,16 @@ FR_EXPORT int residual_post_norm_add(const float* x, const float* y, const void*
                                      cudaStream_t stream) {
     if (n_rows <= 0) return FR_OK;
     const FrVec wv{w, w_dtype}, w2v{w2, w2_dtype};
-    if (next == nullptr || next_dtype == FR_F32)
+    const bool pieces = width % 4 == 0 && width <= 8192 &&
+                        ((((uintptr_t)x) | ((uintptr_t)y) | ((uintptr_t)out) | ((uintptr_t)next)) & 15) == 0;
+#define POST_VEC(TO, NV)                                                                                                           \
+    FR_CUDA(fr_launch(post_norm_add_vec_kernel<TO, NV>, dim3(n_rows), dim3(256), 0, stream, x, y, wv, eps, mult, out, w2v, eps2, (TO*)next, width))
+    if (pieces && (next == nullptr || next_dtype == FR_F32)) {
+        if (width <= 2048) POST_VEC(float, 2); else if (width <= 4096) POST_VEC(float, 4); else POST_VEC(float, 8);
+    } else if (pieces && next_dtype == FR_BF16) {
+        if (width <= 2048) POST_VEC(bf16, 2); else if (width <= 4096) POST_VEC(bf16, 4); else POST_VEC(bf16, 8);
+    } else if (next == nullptr || next_dtype == FR_F32)
+#undef POST_VEC
         FR_CUDA(fr_launch(post_norm_add_kernel<float>, dim3(n_rows), dim3(256), 0, stream, x, y, wv, eps, mult, out, w2v, eps2, (float*)next, width));
     else if (next_dtype == FR_BF16)
         FR_CUDA(fr_launch(post_norm_add_kernel<bf16>, dim3(n_rows), dim3(256), 0, stream, x, y, wv, eps, mult, out, w2v, eps2, (bf16*)next, width));
@@ -595,6 +757,15 @@ FR_EXPORT int residual_post_norm_add(const float* x, const float* y, const void*
 FR_EXPORT int residual_two_sided_act(void* z, long long n, int dtype, const void* pq, int pq_dtype, cudaStream_t stream) {
     if (n <= 0) return FR_OK;
     const FrVec v{pq, pq_dtype};
+    const long long per = dtype == FR_F32 ? 4 : 8;
+    if ((dtype == FR_F32 || dtype == FR_BF16) && n % per == 0 && ((uintptr_t)z & 15) == 0) {
+        const long long pieces = n / per;
+        const unsigned vb = (unsigned)((pieces + 255) / 256 < 148 * 16 ? (pieces + 255) / 256 : 148 * 16);
+        if (dtype == FR_F32) FR_CUDA(fr_launch(two_sided_act_vec_kernel<float>, dim3(vb), dim3(256), 0, stream, (float*)z, pieces, v));
+        else FR_CUDA(fr_launch(two_sided_act_vec_kernel<bf16>, dim3(vb), dim3(256), 0, stream, (bf16*)z, pieces, v));
+        FR_CHECK_LAUNCH("two_sided_act");
+        return FR_OK;
+    }
     const unsigned blocks = (unsigned)((n + 1023) / 1024 < 4096 ? (n + 1023) / 1024 : 4096);
     if (dtype == FR_F32) FR_CUDA(fr_launch(two_sided_act_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)z, n, v));
     else if (dtype == FR_BF16) FR_CUDA(fr_launch(two_sided_act_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (bf16*)z, n, v));
