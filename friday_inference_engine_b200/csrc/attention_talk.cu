@@ -797,7 +797,7 @@ __device__ __forceinline__ void ldsm4_trans(uint32_t (&r)[4], const void* p) {
 // by cp.async in the other of two buffers meanwhile, as they lie in the cache ([key][channel]); ldmatrix.trans makes the
 // B fragments of them.
 template <int DV>
-__global__ void __launch_bounds__(128, 2) talk_prompt_values_kernel(PromptArgs p) {
+__global__ void __launch_bounds__(128, 3) talk_prompt_values_kernel(PromptArgs p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int BM = 64, LV = DV + 8;
     bf16* sv = (bf16*)smem_raw;                                     // [2][PB][LV]
