@@ -22,6 +22,7 @@
 //            sequence x 64 keys per block; the mixing happens in the accumulators' registers, the weights enter the
 //            second product as two bf16 numbers each (head + remainder), which keeps them 32-bit in effect
 #include <math.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -278,7 +279,7 @@ __device__ __forceinline__ void load_pair(const bf16* p, float& a, float& b) {
 
 // The same block of work with the keys and values of its `ks` keys (a multiple of four, at most KS) brought into shared
 // memory first: every thread issues its 16-byte copies at once, so the block's whole share of the cache is in flight
-// together, and queries and the mixing matrix are read meanwhile.  256 threads: four lanes per key for the scores, a
+// together, and queries and the mixing matrix are read meanwhile.  256 threads: 256 / ks lanes per key (four at 64) for the scores, a
 // thread per pair of value channels of a key head for the weighted values.  A key's row in shared memory is 64 bytes
 // longer than its channels, so that the 16-byte reads of two neighbouring keys fall on different banks.
 template <typename T>
@@ -324,8 +325,9 @@ __global__ void __launch_bounds__(256) talk_staged_kernel(SplitArgs p) {
         for (int i = tid; i < H * H; i += 256) tk[i] = p.talk.at(i);
     cp_wait<0>();
     __syncthreads();
-    const int c4 = tid & 3, nchunks = dim / VEC;
-    for (int t = tid >> 2; t < ks; t += 64) {
+    const int lpk = ks >= 64 ? 4 : 256 / ks;                        // lanes that share a key: 4, 8 or 16
+    const int c4 = tid % lpk, nchunks = dim / VEC;
+    for (int t = tid / lpk; t < ks; t += 256 / lpk) {
         const float dist = (float)(pos - (j0 + t0 + t));
         const T* krow = kt + (size_t)t * krow_len;
         for (int g = 0; g < G; ++g) {
@@ -333,7 +335,7 @@ __global__ void __launch_bounds__(256) talk_staged_kernel(SplitArgs p) {
                 float acc[8];
 #pragma unroll
                 for (int a = 0; a < 8; ++a) acc[a] = 0.f;
-                for (int ci = c4; ci < nchunks; ci += 4) {
+                for (int ci = c4; ci < nchunks; ci += lpk) {
                     float kf[VEC];
                     Chunk<T, VEC>::load(krow + (size_t)g * dim + ci * VEC, kf);
 #pragma unroll
@@ -354,8 +356,7 @@ __global__ void __launch_bounds__(256) talk_staged_kernel(SplitArgs p) {
                 for (int a = 0; a < 8; ++a) {
                     if (hc + a < per) {
                         float s = acc[a];
-                        s += __shfl_xor_sync(0xffffffffu, s, 1);
-                        s += __shfl_xor_sync(0xffffffffu, s, 2);
+                        for (int o = lpk >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
                         if (c4 == 0) {
                             const int h = g * per + hc + a;
                             s *= p.scale;
@@ -576,9 +577,15 @@ FR_EXPORT int attention_talk_rows(const void* q, int q_ld, const void* k_pool, c
     const size_t room = 200 * 1024;
     int ks = 0;
     if (k_pieces && v_pieces) {
-        ks = KS;
+        // FRIDAY_TALK_KEYS=16|32|64 forces the keys per block where they fit (for sweeps)
+        static const int forced = [] {
+            const char* e = getenv("FRIDAY_TALK_KEYS");
+            const int v = e != nullptr ? atoi(e) : 0;
+            return v == 16 || v == 32 || v == 64 ? v : 0;
+        }();
+        ks = forced > 0 ? forced : KS;
         while (ks > KS_MIN && (staged_bytes(ks, heads, kv_heads, dim, vdim, esz) > room ||
-                               (long long)n_rows * ((span + ks - 1) / ks) < 222))
+                               (forced == 0 && (long long)n_rows * ((span + ks - 1) / ks) < 222)))
             ks /= 2;
         if (staged_bytes(ks, heads, kv_heads, dim, vdim, esz) > room) ks = 0;
     }
