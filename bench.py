@@ -553,10 +553,10 @@ def ditenex_config(width, layers=7, vocab=32768, window=1024, experts=8, top=2):
              "mask": {"size": window}, "v_mix": True}
     dense = {"kind": "dense", "ff": 3 * width}
     moe = {"kind": "moe", "expert": {"ff": width}, "shared": {"ff": width},
-           "router": {"experts": experts, "top": top, "scale": 1.5, "groups": {"count": 4, "keep": 2}}}
+           "router": {"experts": experts, "top": top, "scale": 2.0, "groups": {"count": 4, "keep": 2}}}
     ls = [{"type": "attention", "mixer": mixer, "mlp": dense if i % 2 == 0 else moe} for i in range(layers)]
-    return {"architecture": "Ditenex", "vocab": vocab, "width": width, "max_positions": 4096, "residual_mult": 0.5,
-            "norm": {"eps": 1e-6}, "layers": ls}
+    return {"architecture": "Ditenex", "vocab": vocab, "width": width, "max_positions": 4096, "residual_mult": 0.7,
+            "norm": {"eps": 1e-5}, "layers": ls}
 
 
 def ditenex_numbers(cfg, batch, context, prompt_len):

@@ -368,7 +368,7 @@ Tensor Ops::talk_attention(const Tensor& proj, const TalkSpec& s, const CacheVie
     // keep what the blocks leave below a gigabyte
     const int64_t per_row = std::max<int64_t>(1, k.scratch_floats(1, s.heads, s.vdim, s.window, ctx.max_kv_len));
     int64_t run = std::max<int64_t>(1, ((int64_t)1 << 28) / per_row);
-    run = std::min(run, rows);
+    run = std::min(std::min(run, rows), (int64_t)65535);      // a row is a block index in y
     float* scratch = scratch_floats(run * per_row);
     for (int64_t r0 = 0; r0 < rows; r0 += run) {
         const int n = (int)std::min(run, rows - r0);
