@@ -86,12 +86,22 @@ Json read_ditenex(const Json& d) {
     if (!(number(member(d, "norm", ""), "eps", "norm: ") > 0)) throw ConfigError("config.json: norm: 'eps' must be positive");
     const Json& layers = member(d, "layers", "");
     if (!layers.is_array() || layers.size() == 0) throw ConfigError("config.json: 'layers' must be a list of at least one layer");
+    int64_t first_values = -1;                   // kv_heads * vdim of the first layer that blends values
     for (size_t i = 0; i < layers.size(); ++i) {
         const std::string where = format("layers[%zu]: ", i);
         const Json& type = member(layers[i], "type", where);
         if (type.as_string() != "attention")
             throw ConfigError("config.json: " + where + "mixer type '" + type.as_string() + "' is not one this design has (attention)");
-        check_attention(member(layers[i], "mixer", where), where + "mixer: ");
+        const Json& mixer = member(layers[i], "mixer", where);
+        check_attention(mixer, where + "mixer: ");
+        if (flag(mixer, "v_mix")) {
+            // blended values are the first blending layer's, element by element: the rows must be as long
+            const int64_t row = mixer.at("kv_heads").as_int() * mixer.at("vdim").as_int();
+            if (first_values < 0) first_values = row;
+            else if (row != first_values)
+                throw ConfigError(format("config.json: %smixer: v_mix blends rows of kv_heads * vdim = %lld with the first such layer's %lld",
+                                         where.c_str(), (long long)row, (long long)first_values));
+        }
         const Json* mlp = layers[i].find("mlp");
         if (mlp && !mlp->is_null()) check_mlp(*mlp, where + "mlp: ");
     }

@@ -77,6 +77,10 @@ CONFIGS = {
     "experts_only": config(64, 100, [(att(1, 1, 8, 8, 1, 0.3), moe(8, 3, 16, 1.7, (4, 2), 24))], 0.8),
     # one wide window (a key hundreds of tokens back), one narrow one
     "far": config(64, 120, [(att(4, 2, 16, 16, 400, 0.25, True), dense(32)), (att(2, 1, 16, 32, 50, 0.25, True), None)], 0.6),
+    # head counts between the powers of two, up to 32, with keys and values in eights (the tensor cores' prompt kernels pad them)
+    "V": config(160, 250, [(att(12, 4, 16, 40, 45, 0.25, True), dense(72)),
+                           (att(20, 5, 8, 32, 70, 0.35, True), moe(6, 2, 24, 1.2, (3, 2), 16)),
+                           (att(32, 8, 8, 8, 64, 0.35), None)], 0.9),
 }
 SEEDS = {name: 170 + i for i, name in enumerate(CONFIGS)}
 

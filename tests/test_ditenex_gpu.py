@@ -104,7 +104,7 @@ def test_each_mechanism_alone(root, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name,n", [("P", 200), ("Q", 70), ("R", 400), ("S", 150), ("T", 200), ("U", 260)])
+@pytest.mark.parametrize("name,n", [("P", 200), ("Q", 70), ("R", 400), ("S", 150), ("T", 200), ("U", 260), ("V", 170)])
 def test_whole_prompt(root, name, n, dtype):
     eng, cfg, _ = engine(root, name, dtype)
     (p,) = prompts([n], cfg["vocab"], 5)
@@ -116,7 +116,7 @@ def test_whole_prompt(root, name, n, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["P", "R", "S", "T", "U"])
+@pytest.mark.parametrize("name", ["P", "R", "S", "T", "U", "V"])
 def test_prompt_then_token_by_token(root, name, dtype):
     """The last tokens one by one, across page borders of 64 and with the windows moving over decoded tokens: keys,
     values and the shift's row go from step to step."""
@@ -175,7 +175,7 @@ def test_passes_of_the_step_function(root, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["P", "R", "S"])
+@pytest.mark.parametrize("name", ["P", "R", "S", "V"])
 def test_batch_of_unequal_requests(root, name, dtype):
     """Requests of different lengths in one batch (one of a single token), then decoded together; the shorter ones
     end earlier.  Every request must come out as it does alone."""
