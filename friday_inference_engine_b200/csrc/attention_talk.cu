@@ -675,15 +675,12 @@ struct PromptArgs {
 };
 
 // 16 rows of a sequence, one block of 64 keys, every head.  The rows' queries are staged once for all heads; each of the
-// 8 / NB warps owns 8 * NB of the keys and keeps scale * q.k - slope * distance of all heads in its accumulators (m16n8k16
-// with the channels of a group of 32 dealt out so that a thread's 16-byte read of a query row and of its key are its A and
-// B fragments of two steps: a product does not care in which order its channels are summed, only that A and B agree).  A
-// query fragment read from shared memory serves NB groups of eight keys (NB = 2 needs the accumulators of all heads twice:
-// up to 16 heads).  The heads are then mixed in the registers, the matrix read from shared memory, and the mixed
-// scores stored.
-template <int HP, int NB>
-__global__ void __launch_bounds__(256 / NB, NB == 2 ? 3 : (HP <= 16 ? 2 : 1)) talk_prompt_scores_kernel(PromptArgs p) {
-    constexpr int NT = 256 / NB;
+// eight warps owns 8 of the keys and keeps scale * q.k - slope * distance of all heads in its accumulators (m16n8k16 with
+// the channels of a group of 32 dealt out so that a thread's 16-byte read of a query row and of its key are its A and B
+// fragments of two steps: a product does not care in which order its channels are summed, only that A and B agree).
+// The heads are then mixed in the registers, the matrix read from shared memory, and the mixed scores stored.
+template <int HP>
+__global__ void __launch_bounds__(256, HP <= 16 ? 2 : 1) talk_prompt_scores_kernel(PromptArgs p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int H = p.heads, per = H / p.kv_heads, dim = p.dim, G = p.kv_heads;
     const int lq = p.q_ld_s;
@@ -699,16 +696,16 @@ __global__ void __launch_bounds__(256 / NB, NB == 2 ? 3 : (HP <= 16 ? 2 : 1)) ta
     const int b = lo0 / PB + blockIdx.x;
     if (b > last_pos / PB) return;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gid = lane >> 2, t4 = lane & 3;
-    for (int i = tid; i < HP * HP; i += NT) {
+    for (int i = tid; i < HP * HP; i += 256) {
         const int h = i / HP, g = i - h * HP;
         tk[i] = (h < H && g < H) ? (p.talk.p != nullptr ? p.talk.at(h * H + g) : (h == g ? 1.f : 0.f)) : 0.f;
     }
-    for (int i = tid; i < HP; i += NT) sl[i] = (i < H && p.slopes != nullptr) ? p.slopes[i] : 0.f;
+    for (int i = tid; i < HP; i += 256) sl[i] = (i < H && p.slopes != nullptr) ? p.slopes[i] : 0.f;
     fr_pdl_wait();
     fr_pdl_launch();
     const int row0 = p.seq_start[seq] + q0;
     const int cpr = H * dim / 8;                                     // 16-byte pieces per row
-    for (int idx = tid; idx < QR * cpr; idx += NT) {
+    for (int idx = tid; idx < QR * cpr; idx += 256) {
         const int r = idx / cpr, c = (idx - r * cpr) * 8;
         uint4 v = make_uint4(0, 0, 0, 0);
         if (r < n_rows) v = *(const uint4*)(p.q + (size_t)(row0 + r) * p.q_ld + c);
@@ -716,35 +713,27 @@ __global__ void __launch_bounds__(256 / NB, NB == 2 ? 3 : (HP <= 16 ? 2 : 1)) ta
     }
     __syncthreads();
     const int page = p.table[(size_t)seq * p.table_width + b];
-    const int wkey = warp * 8 * NB;                                  // the warp's first key within the block
-    // group nb's key whose channels this thread reads: wkey + nb * 8 + gid
-    const bf16* krow = p.k_pool + ((size_t)page * PB + wkey + gid) * G * dim;
-    bool key_ok[NB];
-#pragma unroll
-    for (int nb = 0; nb < NB; ++nb) key_ok[nb] = b * PB + wkey + nb * 8 + gid <= last_pos;
+    const int key = b * PB + warp * 8 + gid;                        // the key whose channels this thread reads
+    const bf16* krow = p.k_pool + ((size_t)page * PB + warp * 8 + gid) * G * dim;
+    const bool key_ok = key <= last_pos;
     const bf16* qa_row = sq + (size_t)gid * lq + t4 * 8;
     const bf16* qb_row = qa_row + (size_t)8 * lq;
-    float acc[HP][NB][4];
+    float acc[HP][4];
 #pragma unroll
-    for (int h = 0; h < HP; ++h)
-#pragma unroll
-        for (int nb = 0; nb < NB; ++nb) acc[h][nb][0] = acc[h][nb][1] = acc[h][nb][2] = acc[h][nb][3] = 0.f;
+    for (int h = 0; h < HP; ++h) acc[h][0] = acc[h][1] = acc[h][2] = acc[h][3] = 0.f;
     const int nch = (dim + 31) / 32;
     for (int c = 0; c < nch; ++c) {
         const int ch = c * 32 + t4 * 8;                             // this thread's eight channels of the group
         const bool ch_ok = ch < dim;
-        uint4 kf[NB];
+        uint4 kf = make_uint4(0, 0, 0, 0);
         int left = 0;                                               // heads that still use the key head in kf
         const bf16* kg = krow + ch;
 #pragma unroll
         for (int h = 0; h < HP; ++h) {
             if (h < H) {
                 if (left == 0) {
-#pragma unroll
-                    for (int nb = 0; nb < NB; ++nb) {
-                        kf[nb] = make_uint4(0, 0, 0, 0);
-                        if (key_ok[nb] && ch_ok) kf[nb] = *(const uint4*)(kg + (size_t)nb * 8 * G * dim);
-                    }
+                    kf = make_uint4(0, 0, 0, 0);
+                    if (key_ok && ch_ok) kf = *(const uint4*)kg;
                     kg += dim;
                     left = per;
                 }
@@ -755,57 +744,51 @@ __global__ void __launch_bounds__(256 / NB, NB == 2 ? 3 : (HP <= 16 ? 2 : 1)) ta
                     qb = *(const uint4*)(qb_row + (size_t)h * dim + c * 32);
                 }
                 const uint32_t a1[4] = {qa.x, qb.x, qa.y, qb.y}, a2[4] = {qa.z, qb.z, qa.w, qb.w};
-#pragma unroll
-                for (int nb = 0; nb < NB; ++nb) {
-                    mma_bf16(acc[h][nb], a1, kf[nb].x, kf[nb].y);
-                    mma_bf16(acc[h][nb], a2, kf[nb].z, kf[nb].w);
-                }
+                mma_bf16(acc[h], a1, kf.x, kf.y);
+                mma_bf16(acc[h], a2, kf.z, kf.w);
             }
         }
     }
+    // accumulator places: (row gid, keys 2 t4 and 2 t4 + 1), (row gid + 8, the same keys)
+    const int col = warp * 8 + 2 * t4;
+    const float d0 = (float)(pos0 + gid - (b * PB + col));          // row gid's distance to its first key; row gid + 8: d0 + 8
+#pragma unroll
+    for (int h = 0; h < HP; ++h) {
+        const float s = sl[h];
+        acc[h][0] = acc[h][0] * p.scale - s * d0;
+        acc[h][1] = acc[h][1] * p.scale - s * (d0 - 1.0f);
+        acc[h][2] = acc[h][2] * p.scale - s * (d0 + 8.0f);
+        acc[h][3] = acc[h][3] * p.scale - s * (d0 + 7.0f);
+    }
+    float* dst[2];
+    bool live[2];
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = gid + 8 * half, pos = pos0 + r;
+        const int first = p.window > 0 ? max(0, pos - p.window + 1) / PB : 0;
+        live[half] = r < n_rows && b >= first && b <= pos / PB;     // else the row sees nothing of this block
+        dst[half] = p.mixed + (size_t)(row0 + r) * H * p.stride + (ptrdiff_t)(b - first) * PB + col;
+    }
     const bool mix = p.talk.p != nullptr;
 #pragma unroll
-    for (int nb = 0; nb < NB; ++nb) {
-        // accumulator places: (row gid, keys 2 t4 and 2 t4 + 1), (row gid + 8, the same keys)
-        const int col = wkey + nb * 8 + 2 * t4;
-        const float d0 = (float)(pos0 + gid - (b * PB + col));      // row gid's distance to its first key; row gid + 8: d0 + 8
+    for (int h = 0; h < HP; ++h) {
+        if (h < H) {
+            float m[4] = {acc[h][0], acc[h][1], acc[h][2], acc[h][3]};
+            if (mix) {
+                m[0] = m[1] = m[2] = m[3] = 0.f;
 #pragma unroll
-        for (int h = 0; h < HP; ++h) {
-            const float s = sl[h];
-            acc[h][nb][0] = acc[h][nb][0] * p.scale - s * d0;
-            acc[h][nb][1] = acc[h][nb][1] * p.scale - s * (d0 - 1.0f);
-            acc[h][nb][2] = acc[h][nb][2] * p.scale - s * (d0 + 8.0f);
-            acc[h][nb][3] = acc[h][nb][3] * p.scale - s * (d0 + 7.0f);
-        }
-        float* dst[2];
-        bool live[2];
+                for (int g4 = 0; g4 < HP; g4 += 4) {
+                    const float4 w = *(const float4*)(tk + h * HP + g4);
+                    const float wa[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-            const int r = gid + 8 * half, pos = pos0 + r;
-            const int first = p.window > 0 ? max(0, pos - p.window + 1) / PB : 0;
-            live[half] = r < n_rows && b >= first && b <= pos / PB;     // else the row sees nothing of this block
-            dst[half] = p.mixed + (size_t)(row0 + r) * H * p.stride + (ptrdiff_t)(b - first) * PB + col;
-        }
+                    for (int a = 0; a < 4; ++a) {
 #pragma unroll
-        for (int h = 0; h < HP; ++h) {
-            if (h < H) {
-                float m[4] = {acc[h][nb][0], acc[h][nb][1], acc[h][nb][2], acc[h][nb][3]};
-                if (mix) {
-                    m[0] = m[1] = m[2] = m[3] = 0.f;
-#pragma unroll
-                    for (int g4 = 0; g4 < HP; g4 += 4) {
-                        const float4 w = *(const float4*)(tk + h * HP + g4);
-                        const float wa[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-                        for (int a = 0; a < 4; ++a) {
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) m[e] = fmaf(wa[a], acc[g4 + a][nb][e], m[e]);
-                        }
+                        for (int e = 0; e < 4; ++e) m[e] = fmaf(wa[a], acc[g4 + a][e], m[e]);
                     }
                 }
-                if (live[0]) *(float2*)(dst[0] + (size_t)h * p.stride) = make_float2(m[0], m[1]);
-                if (live[1]) *(float2*)(dst[1] + (size_t)h * p.stride) = make_float2(m[2], m[3]);
             }
+            if (live[0]) *(float2*)(dst[0] + (size_t)h * p.stride) = make_float2(m[0], m[1]);
+            if (live[1]) *(float2*)(dst[1] + (size_t)h * p.stride) = make_float2(m[2], m[3]);
         }
     }
 }
@@ -866,39 +849,51 @@ __global__ void __launch_bounds__(128, 3) talk_prompt_values_kernel(PromptArgs p
         }
         cp_commit();
     };
-    auto scores = [&](int b, float (&s)[PB / 8][4]) {
+    // the scores of block b as they lie in memory: loads only, nothing depends on them until `finish` (a block later)
+    auto fetch = [&](int b, float2 (&raw)[PB / 8][2]) {
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
             const int pos = my_pos[half], first = my_first[half];
             const bool any = pos >= 0 && b >= first / PB && b <= pos / PB;
-            const bool whole = b * PB >= first && b * PB + PB - 1 <= pos;          // the row sees every key of the block
             const float* src = my_s[half] + (ptrdiff_t)(b - first / PB) * PB;
 #pragma unroll
             for (int nt = 0; nt < PB / 8; ++nt) {
-                float2 v = make_float2(-INFINITY, -INFINITY);
-                if (any) {
-                    v = *(const float2*)(src + nt * 8);
-                    if (!whole) {
-                        const int j = b * PB + nt * 8 + 2 * t;
-                        if (j > pos || j < first) v.x = -INFINITY;
-                        if (j + 1 > pos || j + 1 < first) v.y = -INFINITY;
-                    }
+                raw[nt][half] = make_float2(-INFINITY, -INFINITY);
+                if (any) raw[nt][half] = *(const float2*)(src + nt * 8);
+            }
+        }
+    };
+    // masked by position and scaled for a softmax on powers of two
+    auto finish = [&](int b, const float2 (&raw)[PB / 8][2], float (&s)[PB / 8][4]) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int pos = my_pos[half], first = my_first[half];
+            const bool whole = b * PB >= first && b * PB + PB - 1 <= pos;          // the row sees every key of the block
+#pragma unroll
+            for (int nt = 0; nt < PB / 8; ++nt) {
+                float2 v = raw[nt][half];
+                if (!whole) {
+                    const int j = b * PB + nt * 8 + 2 * t;
+                    if (j > pos || j < first) v.x = -INFINITY;
+                    if (j + 1 > pos || j + 1 < first) v.y = -INFINITY;
                 }
-                s[nt][2 * half] = v.x * LOG2E;                      // the softmax runs on powers of two
+                s[nt][2 * half] = v.x * LOG2E;
                 s[nt][2 * half + 1] = v.y * LOG2E;
             }
         }
     };
 
-    float s[PB / 8][4], s_next[PB / 8][4];
+    float s[PB / 8][4];
+    float2 raw[PB / 8][2];
     stage(b_lo, 0);
-    scores(b_lo, s);
+    fetch(b_lo, raw);
+    finish(b_lo, raw, s);
     for (int b = b_lo; b <= b_hi; ++b) {
         const int buf = (b - b_lo) & 1;
         const bool more = b < b_hi;
         if (more) {
             stage(b + 1, buf ^ 1);
-            scores(b + 1, s_next);
+            fetch(b + 1, raw);
             cp_wait<1>();
         } else {
             cp_wait<0>();
@@ -956,12 +951,7 @@ __global__ void __launch_bounds__(128, 3) talk_prompt_values_kernel(PromptArgs p
             }
         }
         __syncthreads();                                            // the buffer is free for the block after next
-        if (more) {
-#pragma unroll
-            for (int nt = 0; nt < PB / 8; ++nt)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) s[nt][e] = s_next[nt][e];
-        }
+        if (more) finish(b + 1, raw, s);
     }
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
@@ -1014,13 +1004,13 @@ size_t prompt_scores_smem(int heads, int dim) {
     return ((size_t)hp * hp + hp) * sizeof(float) + (size_t)QR * staged_row(heads, dim) * sizeof(bf16);
 }
 
-template <int HP, int NB>
+template <int HP>
 int launch_scores(const PromptArgs& p, int n_seqs, int max_q_len, cudaStream_t stream) {
     const size_t smem = prompt_scores_smem(p.heads, p.dim);
-    FR_CUDA(cudaFuncSetAttribute(talk_prompt_scores_kernel<HP, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    FR_CUDA(cudaFuncSetAttribute(talk_prompt_scores_kernel<HP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     // a tile of 16 rows sees at most one block more than a single row does
     const dim3 grid((unsigned)(p.stride / PB + 1), (unsigned)((max_q_len + QR - 1) / QR), (unsigned)n_seqs);
-    FR_CUDA(fr_launch(talk_prompt_scores_kernel<HP, NB>, grid, dim3(256 / NB), smem, stream, p));
+    FR_CUDA(fr_launch(talk_prompt_scores_kernel<HP>, grid, dim3(256), smem, stream, p));
     FR_CHECK_LAUNCH("talk prompt scores");
     return FR_OK;
 }
@@ -1057,15 +1047,8 @@ FR_EXPORT int attention_talk_prompt(const void* q, int q_ld, const void* k_pool,
     p.stride = prompt_stride(window, max_kv_len); p.scale = scale; p.slopes = slopes; p.talk = FrVec{talk, talk_dtype};
     p.gate = (const bf16*)gate; p.gate_ld = gate_ld; p.out = (bf16*)out; p.mixed = scratch;
     const int hp = padded_heads(heads);
-    // FRIDAY_TALK_GROUPS=2 gives every warp two groups of eight keys (up to 16 heads), so that a query fragment serves
-    // two products: measured level with one group at 16 heads of 128, kept for comparisons
-    static const bool two_groups = [] {
-        const char* e = getenv("FRIDAY_TALK_GROUPS");
-        return e != nullptr && e[0] == '2';
-    }();
-    const int rc = hp == 8 ? (two_groups ? launch_scores<8, 2>(p, n_seqs, max_q_len, stream) : launch_scores<8, 1>(p, n_seqs, max_q_len, stream))
-                 : hp == 16 ? (two_groups ? launch_scores<16, 2>(p, n_seqs, max_q_len, stream) : launch_scores<16, 1>(p, n_seqs, max_q_len, stream))
-                 : launch_scores<32, 1>(p, n_seqs, max_q_len, stream);
+    const int rc = hp == 8 ? launch_scores<8>(p, n_seqs, max_q_len, stream)
+                 : hp == 16 ? launch_scores<16>(p, n_seqs, max_q_len, stream) : launch_scores<32>(p, n_seqs, max_q_len, stream);
     if (rc != FR_OK) return rc;
     if (vdim <= 32) return launch_values<32>(p, n_seqs, max_q_len, stream);
     if (vdim <= 64) return launch_values<64>(p, n_seqs, max_q_len, stream);
