@@ -7,20 +7,23 @@
 //   out_h(i)      = sum_j softmax_j(mixed_h(i, .))[j] * v_kv(h)(j)   (* sigmoid(gate_h(i)) element by element, if given)
 //
 // A head's softmax needs every head's score of the same (i, j), so the work is cut across the keys and not across the
-// heads: `scores` computes the raw scores of ALL heads for a block of keys, mixes them and writes the mixed scores
-// [row][head][slot] (slot t of a row at position i is the key j = max(0, i - window + 1) + t); `values` runs each
-// head's softmax over its slots and multiplies with the values.  Scores, the mixing, the softmax and its weights are
-// fp32 in both dtypes; keys, values and queries are read in the dtype they are stored in.
+// heads: a block owns some keys of a row (or of 16 rows) and ALL heads, computes the raw scores, and mixes them.  Scores,
+// the mixing, the softmax and its weights are fp32 in both dtypes; keys, values and queries are read in the dtype they are
+// stored in.
 //
 //   store    keys and values of the step's rows go to their cache rows; values may first be blended with rows that
 //            another layer left for the same tokens, v <- (1 - lambda) v + lambda v_first (the blended rows are what is
 //            kept), and a layer may leave its values for later layers
-//   scores   CUDA cores: a block per (row, 128 keys), a thread per key, the key tile staged 32 channels at a time
-//   values   CUDA cores: a block per (row, kv head); a warp per head finds maximum and sum, then all threads walk the
-//            keys with the weights of up to four heads in shared memory, a value channel (or two) per thread
-//   scores_mma / values_mma   bfloat16 prompts: the same two steps on the tensor cores (mma.sync.m16n8k16), 16 rows of a
-//            sequence x 64 keys per block; the mixing happens in the accumulators' registers, the weights enter the
-//            second product as two bf16 numbers each (head + remainder), which keeps them 32-bit in effect
+//   staged   single rows and everything in float32, CUDA cores: a block per (row, 16, 32 or 64 keys) brings its keys and
+//            values into shared memory with all copies in flight at once, then scores of all heads, the mixing, each
+//            head's maximum and sum, and the weighted values of the block's keys; `split` is the same block reading the
+//            cache as it goes, for rows of keys or values that are not whole 16-byte pieces
+//   merge    a block per (head, row) joins what the row's blocks left (maximum / sum rule) and applies the gate
+//   prompt_scores / prompt_values   bfloat16 prompts on the tensor cores (mma.sync.m16n8k16): 16 rows of a sequence x 64
+//            keys x all heads per block, the mixing in the accumulators' registers, the mixed scores through memory once
+//            ([row][head][keys in sight] floats); then 64 rows x one head per block run the softmax block of keys by
+//            block of keys and enter the weights into the second product as two bf16 numbers each (head + remainder),
+//            which keeps them 32-bit in effect
 #include <math.h>
 #include <stdlib.h>
 
