@@ -565,10 +565,11 @@ FR_EXPORT int routed_combine(const float* part, const int* ids, const float* wei
 }
 
 // ------------------------------------------------------------------ a choice by biased sigmoid scores among groups of experts
-// Per row: s_e = sigmoid(z_e); the choice runs on c_e = s_e + bias_e (bias null: none).  The experts form `groups` equal
-// groups of neighbours; a group's score is the sum of its two largest c (of its one, if groups are single experts); only the
-// `keep` best groups' experts can be chosen (the others count as minus infinity).  The `top` largest c are chosen (the lower
-// index wins a tie, among groups as among experts); the weights are s_e * scale of the chosen, not renormalised.  fp32.
+// Per row: s_e = sigmoid(z_e) and c_e = s_e + bias_e (bias null: c = s).  Experts e with the same e / (experts / groups)
+// are one group, ranked by r = the two largest c of the group added up (one c, if a group is a single expert).  Outside
+// the `keep` groups of highest r an expert cannot win (its c reads as -inf, so negative c inside still beat it).  The `top`
+// experts of highest c win (ties: the lower index, for groups and experts alike) with weight s_e * scale; the weights are
+// left as they are, they need not sum to one.  fp32.
 namespace {
 
 __global__ void __launch_bounds__(128)

@@ -217,7 +217,7 @@ public:
     };
     Routing route(const Tensor& logits, int top, bool softmax_all, bool with_dense);
     // scores sigmoid(logit); the choice runs on score + bias (null: none) among the experts of the `keep` best of `groups`
-    // equal groups of neighbours (a group counts as the sum of its two largest); weights = score * scale of the chosen
+    // equally sized runs of adjacent experts (a group counts as the sum of its two largest); weights = score * scale of the chosen
     Routing route_scored(const Tensor& logits, int top, const Tensor* bias, int groups, int keep, float scale, bool with_dense);
     void scale_by_route(Tensor& act, const Tensor& dense, int experts, int inner);
     Tensor expert_gate_up(const Tensor& h, const Routing& r, const Tensor& w_gate_up, int top, int inner);

@@ -229,7 +229,7 @@ public:
         if (top_ > experts_) throw ConfigError(format("routed_experts: top %d of %d experts", top_, experts_));
         if (top_ > 32 || experts_ > 256) throw ConfigError("routed_experts: at most 256 experts and 32 choices");
         // "score": "sigmoid" makes the scores sigmoid(logit): the choice runs on score + the tensor "choice_bias" (if named)
-        // among the experts of the "groups_keep" best of "groups" equal groups of neighbours (a group counts as the sum of its
+        // among the experts of the "groups_keep" best of "groups" equally sized runs of adjacent experts (a group counts as the sum of its
         // two largest), the weights are score * "weight_scale", not renormalised.  "router_bias": false leaves the logits'
         // bias out.  "shared_inner" > 0 adds an expert of that inner size ("shared.") that every row uses.
         const std::string score = s.params.get_string("score", "softmax");
