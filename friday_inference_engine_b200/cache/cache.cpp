@@ -27,11 +27,11 @@ void FreeList::give(int i) {
 
 KVGroup::KVGroup(const CacheRequest& req, const std::vector<int>& ents, int n_slots, int pages_, int width_, DType dt,
                  bool on_device)
-    : request(req), entries(ents), window(req.window), n_pages(pages_), width(width_), dtype(dt), pages(pages_, "page"),
+    : request(req), entries(ents), window(req.window), n_pages(pages_), width(width_), dtype(req.store_f32 ? DType::F32 : dt), pages(pages_, "page"),
       table((size_t)n_slots * width_, -1) {
     if (on_device) {
         k_pool = DeviceBuffer(entry_bytes() * entries.size());
-        v_pool = DeviceBuffer(value_entry_bytes() * entries.size());
+        if (!req.keys_only) v_pool = DeviceBuffer(value_entry_bytes() * entries.size());
     }
 }
 
@@ -47,11 +47,11 @@ int KVGroup::first_needed_page(int start_pos) const {
 }
 
 std::vector<int> KVGroup::pages_missing(int slot, int start_pos, int new_len) const {
-    if (new_len > width * PAGE)
-        throw CacheError(format("a sequence of %d tokens does not fit the cache's %d tokens per sequence", new_len, width * PAGE));
+    if (rows_for(new_len) > width * PAGE)
+        throw CacheError(format("a sequence of %d tokens does not fit the cache's %d tokens per sequence", new_len, width * PAGE * every()));
     std::vector<int> out;
     const int* row = table_row(slot);
-    const int lo = first_needed_page(start_pos), hi = (new_len + PAGE - 1) / PAGE;
+    const int lo = first_needed_page(start_pos), hi = (rows_for(new_len) + PAGE - 1) / PAGE;
     for (int lp = lo; lp < hi; ++lp)
         if (row[lp] < 0) out.push_back(lp);
     return out;
@@ -100,7 +100,7 @@ Cache::Cache(const std::map<int, CacheRequest>& requests, int64_t max_tokens, in
     // hold more pages than there are, so the table need not be wider than that; with a window it holds few pages
     // at a time but at any logical place.
     const int seq_pages = std::max(1, (max_seq_tokens + PAGE - 1) / PAGE);
-    typedef std::tuple<int, int, int, int, int> Need;
+    typedef std::tuple<int, int, int, int, int, int, int> Need;
     std::vector<std::pair<Need, std::vector<int>>> by_need;          // in order of first appearance
     // a request made of several becomes one request per part, each under a key of its own
     std::map<int, CacheRequest> flat;
@@ -118,7 +118,9 @@ Cache::Cache(const std::map<int, CacheRequest>& requests, int64_t max_tokens, in
     for (const auto& kv : flat) {
         const CacheRequest& r = kv.second;
         if (r.kind == CacheRequest::KV) {
-            const Need need(r.n_kv_heads, r.head_dim, r.window, r.value_dim(), r.keep_first);
+            if (r.every > 1 && r.window > 0) throw CacheError("a cache request with a row per several positions cannot have a window");
+            const Need need(r.n_kv_heads, r.head_dim, r.window, r.value_dim(), r.keep_first, r.every > 1 ? r.every : 1,
+                            (r.keys_only ? 1 : 0) + (r.store_f32 ? 2 : 0));
             auto it = std::find_if(by_need.begin(), by_need.end(), [&](const auto& p) { return p.first == need; });
             if (it == by_need.end()) by_need.emplace_back(need, std::vector<int>{kv.first});
             else it->second.push_back(kv.first);
@@ -135,8 +137,12 @@ Cache::Cache(const std::map<int, CacheRequest>& requests, int64_t max_tokens, in
     }
     for (auto& p : by_need) {
         const CacheRequest req = flat.at(p.second[0]);
-        const int width = req.window > 0 ? seq_pages : std::min(n_pages, seq_pages);
-        groups.emplace_back(new KVGroup(req, p.second, max_slots, n_pages, width, dtype, on_device));
+        // a row per `every` positions: that many times fewer pages, and one more per sequence for the page it has begun
+        const int every = req.every > 1 ? req.every : 1;
+        const int group_pages = every > 1 ? (n_pages + every - 1) / every + max_slots : n_pages;
+        const int group_seq_pages = every > 1 ? std::max(1, ((max_seq_tokens + every - 1) / every + PAGE - 1) / PAGE) : seq_pages;
+        const int width = req.window > 0 ? group_seq_pages : std::min(group_pages, group_seq_pages);
+        groups.emplace_back(new KVGroup(req, p.second, max_slots, group_pages, width, dtype, on_device));
         for (int e : p.second) group_of[e] = (int)groups.size() - 1;
     }
 }
@@ -200,7 +206,8 @@ CacheView Cache::view(int entry, bool write, const std::vector<const int*>& step
         const int i = grp.index_of(entry);
         v.kind = CacheRequest::KV;
         v.k_pool = (char*)grp.k_pool.get() + (size_t)i * grp.entry_bytes();
-        v.v_pool = (char*)grp.v_pool.get() + (size_t)i * grp.value_entry_bytes();
+        v.v_pool = grp.request.keys_only ? v.k_pool : (char*)grp.v_pool.get() + (size_t)i * grp.value_entry_bytes();
+        v.every = grp.every();
         v.pool_pages = grp.n_pages;
         v.block_table = step_tables[g->second];
         v.table_width = grp.width;
@@ -225,8 +232,18 @@ CacheView Cache::view(int entry, bool write, const std::vector<const int*>& step
     return v;
 }
 
+std::vector<CacheView> Cache::program_views(const ModelSpec& spec, const std::vector<const int*>& step_tables, const int* seq_slots_dev) const {
+    std::vector<CacheView> views;
+    for (const auto& call : spec.program)
+        views.push_back(call.cache < 0 ? CacheView() : view(call.cache, call.write, step_tables, seq_slots_dev));
+    if (spec.has_embed_state()) views.push_back(view(ModelSpec::kEmbedStateEntry, true, step_tables, seq_slots_dev));
+    return views;
+}
+
 int64_t Cache::held_tokens() const {
-    return groups.empty() ? 0 : (int64_t)groups[0]->pages.held_count() * PAGE;
+    for (const auto& g : groups)
+        if (g->every() == 1) return (int64_t)g->pages.held_count() * PAGE;      // a group that keeps a row per position
+    return 0;
 }
 
 size_t Cache::bytes() const {

@@ -471,3 +471,241 @@ FR_EXPORT int delta_scan(const float* qkv, const void* a_raw, int ld_a, const vo
     if (raw_dtype == FR_BF16) return scan_by_size<bf16>(p, n_seqs, splits, stream);
     FR_REFUSE("delta scan: unknown dtype %d", raw_dtype);
 }
+
+// ------------------------------------------------------------------ the generalized delta rule
+// A decay per head and key channel and a removal along the unit key, both reading the old state:
+//
+//     S <- diag(w_t) S - (a_t * u_t) (u_t^T S) + k_t v_t^T,   o_t = S^T r_t
+//
+// with u = k / sqrt(sum k^2 + unit_eps) per head, w = exp(-decay_rate * sigmoid(z + z_bias)) and a = sigmoid(a_raw + a_bias),
+// all formed in fp32 by `general_prepare` (one warp per row and head), which leaves per row and head five vectors of dk
+// floats: w, a * u, u, k, r.  `general_scan` walks the tokens of a sequence: four lanes share a value channel (a column of
+// S), each with a quarter of the key channels in registers; the block stages eight tokens at a time through shared memory,
+// the next eight loaded into registers before the present ones are walked.  Columns of S never mix, so any split of the value
+// channels over blocks is exact.  State of a sequence: [heads][dk][dv] fp32 at `s_off`.
+namespace {
+
+struct GeneralPrepArgs {
+    const void* proj;        // [rows][ld]: r at r_off, k at k_off (heads * dk each), in the activation dtype
+    const float* z;          // [rows][ld_z] fp32: the decay's raw projection
+    const float* a_raw;      // [rows][ld_a] fp32: the removal's raw projection
+    FrVec z_bias, a_bias;    // [heads * dk]
+    float* out;              // [rows][heads][5][dk]
+    int ld, r_off, k_off, ld_z, ld_a, heads, dk, rows;
+    float rate, unit_eps;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128) general_prepare_kernel(GeneralPrepArgs p) {
+    fr_pdl_wait();
+    fr_pdl_launch();
+    const int item = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (item >= p.rows * p.heads) return;
+    const int row = item / p.heads, h = item - row * p.heads;
+    const T* x = (const T*)p.proj + (size_t)row * p.ld;
+    float ss = 0.f;
+    for (int i = lane; i < p.dk; i += 32) {
+        const float k = fr_load(x + p.k_off + h * p.dk + i);
+        ss = fmaf(k, k, ss);
+    }
+    const float inv = 1.0f / sqrtf(fr_warp_sum(ss) + p.unit_eps);
+    float* o = p.out + (size_t)item * 5 * p.dk;
+    for (int i = lane; i < p.dk; i += 32) {
+        const int c = h * p.dk + i;
+        const float k = fr_load(x + p.k_off + c), r = fr_load(x + p.r_off + c);
+        const float zz = p.z[(size_t)row * p.ld_z + c] + p.z_bias.at(c);
+        const float aa = p.a_raw[(size_t)row * p.ld_a + c] + p.a_bias.at(c);
+        const float u = k * inv;
+        o[i] = expf(-p.rate / (1.0f + expf(-zz)));
+        o[p.dk + i] = u / (1.0f + expf(-aa));
+        o[2 * p.dk + i] = u;
+        o[3 * p.dk + i] = k;
+        o[4 * p.dk + i] = r;
+    }
+}
+
+struct GeneralScanArgs {
+    const float* prep;       // [rows][heads][5][dk]
+    const void* v;           // [rows][ld_v], head h at v_off + h * dv
+    float* out;              // [rows][heads * dv]
+    float* state;
+    long long state_stride, s_off;
+    const int* seq_start;
+    const int* seq_qlen;
+    const int* seq_slots;
+    int ld_v, v_off, heads, dk, dv, cols;
+};
+
+// tokens staged at a time: fewer where a token is wide, so that what a thread holds of the next chunk stays in registers
+constexpr int gen_tokens(int dkp) { return dkp <= 64 ? 8 : (dkp <= 128 ? 4 : 2); }
+
+// DKP: key channels rounded up to 16, 32, 64, 128 or 256; a lane holds DKP / 4 of them, dealt out in groups of four so that
+// the four lanes of a column read neighbouring 16-byte pieces of shared memory
+template <typename T, int DKP>
+__global__ void __launch_bounds__(128) general_scan_kernel(GeneralScanArgs p) {
+    extern __shared__ __align__(16) float gsm[];
+    constexpr int PER = DKP / 4, VEC = 5 * DKP, GEN_TOKENS = gen_tokens(DKP);
+    const int seq = blockIdx.x, head = blockIdx.y, tid = threadIdx.x, threads = blockDim.x;
+    const int part = tid & 3, local_col = tid >> 2, col = blockIdx.z * p.cols + local_col;
+    const bool live_col = local_col < p.cols && col < p.dv;
+    fr_pdl_wait();
+    fr_pdl_launch();
+    const int n = p.seq_qlen[seq], r0 = p.seq_start[seq];
+    if (n <= 0) return;
+    float* S = p.state + (size_t)p.seq_slots[seq] * p.state_stride + p.s_off + (size_t)head * p.dk * p.dv;
+    float s[PER];
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const int i = 4 * (4 * (j >> 2) + part) + (j & 3);
+        s[j] = (live_col && i < p.dk) ? S[(size_t)i * p.dv + col] : 0.f;
+    }
+    const int buf_floats = GEN_TOKENS * (VEC + p.cols);
+    // what one thread loads of a chunk: vectors (w, a u, u, k, r padded to DKP with zeros) and the block's value channels
+    constexpr int N_IT = (GEN_TOKENS * VEC + 127) / 128;
+    const int n_v = (GEN_TOKENS * p.cols + threads - 1) / threads;          // at most 2 with 32 columns and 128 threads
+    float held[N_IT], held_v[2];
+    auto fetch = [&](int t0) {
+        const int nt = min(GEN_TOKENS, n - t0);
+#pragma unroll
+        for (int it = 0; it < N_IT; ++it) {
+            const int idx = tid + it * threads;
+            const int t = idx / VEC, rest = idx - t * VEC, which = rest / DKP, i = rest - which * DKP;
+            held[it] = (idx < GEN_TOKENS * VEC && t < nt && i < p.dk)
+                           ? p.prep[((size_t)(r0 + t0 + t) * p.heads + head) * 5 * p.dk + (size_t)which * p.dk + i] : 0.f;
+        }
+        for (int it = 0; it < n_v && it < 2; ++it) {
+            const int idx = tid + it * threads;
+            const int t = idx / p.cols, c = idx - t * p.cols;
+            const int cc = blockIdx.z * p.cols + c;
+            held_v[it] = (idx < GEN_TOKENS * p.cols && t < nt && cc < p.dv)
+                             ? fr_load((const T*)p.v + (size_t)(r0 + t0 + t) * p.ld_v + p.v_off + head * p.dv + cc) : 0.f;
+        }
+    };
+    auto put = [&](int b) {
+        float* dst = gsm + (size_t)b * buf_floats;
+#pragma unroll
+        for (int it = 0; it < N_IT; ++it) {
+            const int idx = tid + it * threads;
+            if (idx < GEN_TOKENS * VEC) dst[idx] = held[it];
+        }
+        for (int it = 0; it < n_v && it < 2; ++it) {
+            const int idx = tid + it * threads;
+            if (idx < GEN_TOKENS * p.cols) dst[GEN_TOKENS * VEC + idx] = held_v[it];
+        }
+    };
+    const int chunks = (n + GEN_TOKENS - 1) / GEN_TOKENS;
+    fetch(0);
+    put(0);
+    __syncthreads();
+    for (int c = 0; c < chunks; ++c) {
+        const int t0 = c * GEN_TOKENS, nt = min(GEN_TOKENS, n - t0);
+        if (c + 1 < chunks) fetch(t0 + GEN_TOKENS);
+        const float* buf = gsm + (size_t)(c & 1) * buf_floats;
+        for (int t = 0; t < nt; ++t) {
+            const float4* w4 = (const float4*)(buf + t * VEC) + part;
+            const float4* b4 = w4 + DKP / 4;
+            const float4* u4 = b4 + DKP / 4;
+            const float4* k4 = u4 + DKP / 4;
+            const float4* r4 = k4 + DKP / 4;
+            float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+#pragma unroll
+            for (int m = 0; m < PER / 4; ++m) {
+                const float4 u = u4[4 * m];
+                d0 = fmaf(u.x, s[4 * m], d0);
+                d1 = fmaf(u.y, s[4 * m + 1], d1);
+                d2 = fmaf(u.z, s[4 * m + 2], d2);
+                d3 = fmaf(u.w, s[4 * m + 3], d3);
+            }
+            float dot = (d0 + d1) + (d2 + d3);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+            const float val = buf[GEN_TOKENS * VEC + t * p.cols + (local_col < p.cols ? local_col : 0)];
+            float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+            for (int m = 0; m < PER / 4; ++m) {
+                const float4 w = w4[4 * m], b = b4[4 * m], k = k4[4 * m], r = r4[4 * m];
+                s[4 * m] = fmaf(k.x, val, fmaf(-b.x, dot, w.x * s[4 * m]));
+                s[4 * m + 1] = fmaf(k.y, val, fmaf(-b.y, dot, w.y * s[4 * m + 1]));
+                s[4 * m + 2] = fmaf(k.z, val, fmaf(-b.z, dot, w.z * s[4 * m + 2]));
+                s[4 * m + 3] = fmaf(k.w, val, fmaf(-b.w, dot, w.w * s[4 * m + 3]));
+                o0 = fmaf(r.x, s[4 * m], o0);
+                o1 = fmaf(r.y, s[4 * m + 1], o1);
+                o2 = fmaf(r.z, s[4 * m + 2], o2);
+                o3 = fmaf(r.w, s[4 * m + 3], o3);
+            }
+            float o = (o0 + o1) + (o2 + o3);
+            o += __shfl_xor_sync(0xffffffffu, o, 1);
+            o += __shfl_xor_sync(0xffffffffu, o, 2);
+            if (part == 0 && live_col) p.out[(size_t)(r0 + t0 + t) * ((size_t)p.heads * p.dv) + head * p.dv + col] = o;
+        }
+        if (c + 1 < chunks) put((c + 1) & 1);
+        __syncthreads();
+    }
+    if (live_col) {
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            const int i = 4 * (4 * (j >> 2) + part) + (j & 3);
+            if (i < p.dk) S[(size_t)i * p.dv + col] = s[j];
+        }
+    }
+}
+
+template <typename T, int DKP>
+int launch_general(const GeneralScanArgs& p, int n_seqs, cudaStream_t stream) {
+    const size_t smem = (size_t)2 * gen_tokens(DKP) * (5 * DKP + p.cols) * sizeof(float);
+    if (smem > 48 * 1024) FR_CUDA(cudaFuncSetAttribute(general_scan_kernel<T, DKP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const dim3 grid(n_seqs, p.heads, (p.dv + p.cols - 1) / p.cols);
+    // always 128 threads: those beyond the block's columns only help to stage
+    FR_CUDA(fr_launch(general_scan_kernel<T, DKP>, grid, dim3(128), smem, stream, p));
+    FR_CHECK_LAUNCH("general delta scan");
+    return FR_OK;
+}
+
+template <typename T>
+int general_by_size(const GeneralScanArgs& p, int n_seqs, cudaStream_t stream) {
+    if (p.dk <= 16) return launch_general<T, 16>(p, n_seqs, stream);
+    if (p.dk <= 32) return launch_general<T, 32>(p, n_seqs, stream);
+    if (p.dk <= 64) return launch_general<T, 64>(p, n_seqs, stream);
+    if (p.dk <= 128) return launch_general<T, 128>(p, n_seqs, stream);
+    if (p.dk <= 256) return launch_general<T, 256>(p, n_seqs, stream);
+    FR_REFUSE("general delta scan: %d key channels per head (at most 256)", p.dk);
+}
+
+}  // namespace
+
+// proj [rows][ld] of `dtype` (r at r_off, k at k_off); z [rows][ld_z] and a_raw [rows][ld_a] fp32; biases [heads * dk] of
+// vec_dtype; out [rows][heads][5][dk] fp32 (w, a u, u, k, r)
+FR_EXPORT int delta_general_prepare(const void* proj, int ld, int r_off, int k_off, const float* z, int ld_z, const float* a_raw, int ld_a,
+                                    const void* z_bias, const void* a_bias, int vec_dtype, float* out, int rows, int heads, int dk, float rate,
+                                    float unit_eps, int dtype, cudaStream_t stream) {
+    if (rows <= 0) return FR_OK;
+    if (heads <= 0 || dk <= 0) FR_REFUSE("general delta rule: %d heads of %d", heads, dk);
+    GeneralPrepArgs p;
+    p.proj = proj; p.z = z; p.a_raw = a_raw; p.z_bias = FrVec{z_bias, vec_dtype}; p.a_bias = FrVec{a_bias, vec_dtype}; p.out = out; p.ld = ld;
+    p.r_off = r_off; p.k_off = k_off; p.ld_z = ld_z; p.ld_a = ld_a; p.heads = heads; p.dk = dk; p.rows = rows; p.rate = rate; p.unit_eps = unit_eps;
+    const dim3 grid((unsigned)(((long long)rows * heads + 3) / 4));
+    if (dtype == FR_F32) FR_CUDA(fr_launch(general_prepare_kernel<float>, grid, dim3(128), 0, stream, p));
+    else if (dtype == FR_BF16) FR_CUDA(fr_launch(general_prepare_kernel<bf16>, grid, dim3(128), 0, stream, p));
+    else FR_REFUSE("general delta rule: unknown dtype %d", dtype);
+    FR_CHECK_LAUNCH("general_prepare");
+    return FR_OK;
+}
+
+// prep as general_prepare leaves it; v [rows][ld_v] of `dtype`, head h at v_off + h * dv; out [rows][heads * dv] fp32
+FR_EXPORT int delta_general_scan(const float* prep, const void* v, int ld_v, int v_off, float* out, float* state, long long state_stride,
+                                 long long s_off, const int* seq_start, const int* seq_qlen, const int* seq_slots, int n_seqs, int heads,
+                                 int dk, int dv, int dtype, cudaStream_t stream) {
+    if (n_seqs <= 0) return FR_OK;
+    if (heads <= 0 || dk <= 0 || dv <= 0) FR_REFUSE("general delta scan: %d heads, dk %d, dv %d", heads, dk, dv);
+    GeneralScanArgs p;
+    p.prep = prep; p.v = v; p.out = out; p.state = state; p.state_stride = state_stride; p.s_off = s_off; p.seq_start = seq_start;
+    p.seq_qlen = seq_qlen; p.seq_slots = seq_slots; p.ld_v = ld_v; p.v_off = v_off; p.heads = heads; p.dk = dk; p.dv = dv;
+    const int sms = fr_sm_count() > 0 ? fr_sm_count() : 128;
+    int cols = 32;
+    if ((long long)n_seqs * heads * ((dv + cols - 1) / cols) < 2LL * sms) cols = 16;
+    if (cols > ((dv + 7) / 8) * 8) cols = ((dv + 7) / 8) * 8;
+    p.cols = cols;
+    if (dtype == FR_F32) return general_by_size<float>(p, n_seqs, stream);
+    if (dtype == FR_BF16) return general_by_size<bf16>(p, n_seqs, stream);
+    FR_REFUSE("general delta scan: unknown dtype %d", dtype);
+}

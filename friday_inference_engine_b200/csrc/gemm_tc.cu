@@ -84,7 +84,7 @@ struct GemmParams {
     int* status;        // 0, or a code when a wait gave up
     int p_rows, q_rows, ldo, out_dtype, bias_dtype, swapped;
     int bn;             // rows of Q per tile: the kernel's BN, or any multiple of 16 below it in the widest instance
-    int act;            // 1: the product's columns are (gate, up) pairs; out gets silu(gate) * up, half as wide
+    int act;            // 1, 2: the product's columns are (gate, up) pairs; out gets silu(gate) * up (2: gelu_tanh(gate) * up), half as wide
     int tiles_p, tiles_q, splits, kb_total, kb_per;
     // Work decomposition.  The first dp_tiles tiles are cut into `splits` equal k ranges each and dealt out round
     // robin (splits = 1: whole tiles).  The remaining sk_tiles tiles ("stream-k"): their k blocks, laid end to end,
@@ -441,8 +441,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const float4 a = *(const float4*)(src + 4 * j);
-                x[2 * j] = silu_mul(a.x, a.y);
-                x[2 * j + 1] = silu_mul(a.z, a.w);
+                x[2 * j] = gated_mul(p.act, a.x, a.y);
+                x[2 * j + 1] = gated_mul(p.act, a.z, a.w);
             }
             __nv_bfloat16* out_at = (__nv_bfloat16*)p.out + (size_t)(q_blk * bn + token) * p.ldo + ((p_blk * TILE_P + f0) >> 1);
             *(uint4*)out_at = round8(x);
@@ -1066,7 +1066,7 @@ FR_EXPORT int gemm_tc_fused(const void* x, const void* w, void* out, int out_dty
                             long long scratch_floats, int* counters, int n_counters, int* status, int sm_count,
                             int swap, int bn, int splits, int act, const GemmFusion* fusion, cudaStream_t stream) {
     if (m <= 0 || n <= 0) return FR_OK;
-    if (act != 0 && act != 1) FR_REFUSE("gemm_tc: unknown activation %d", act);
+    if (act < 0 || act > 2) FR_REFUSE("gemm_tc: unknown activation %d", act);
     if (act && (n % 2 || bias != nullptr || residual != nullptr || out_dtype != FR_BF16))
         FR_REFUSE("gemm_tc: the gated epilogue needs an even n, bf16 output, no bias and no residual");
     if (k <= 0 || k % 8 || lda % 8 || ldw % 8)

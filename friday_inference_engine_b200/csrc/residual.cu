@@ -773,3 +773,223 @@ FR_EXPORT int residual_two_sided_act(void* z, long long n, int dtype, const void
     FR_CHECK_LAUNCH("two_sided_act");
     return FR_OK;
 }
+
+// ------------------------------------------------------------------ a hashed token-pair table beside the token table
+// out[row] = table[token] + pairs[r] as 32-bit rows, r = (previous token * mul_prev + token * mul_cur) mod buckets, or row
+// `buckets` (the table's last) for a sequence's first token.  The previous token of a step's first row comes from the
+// sequence's state (one int32 per slot), which then keeps the step's last token: the block of a sequence's first row reads
+// the state before it writes it, and no other block touches it.
+namespace {
+
+template <typename TW>
+__global__ void __launch_bounds__(256)
+embed_pair_kernel(const int* __restrict__ tokens, const int* __restrict__ row_seq, const int* __restrict__ row_pos,
+                  const int* __restrict__ seq_start, const int* __restrict__ seq_qlen, const int* __restrict__ seq_slots,
+                  const TW* __restrict__ table, const TW* __restrict__ pairs, int* __restrict__ state, float* __restrict__ out, int width,
+                  int vocab, int buckets, long long mul_prev, long long mul_cur) {
+    fr_pdl_wait();
+    const int row = blockIdx.x;
+    const int seq = row_seq[row];
+    float* o = out + (size_t)row * width;
+    if (seq < 0) {
+        fr_pdl_launch();
+        for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = 0.f;
+        return;
+    }
+    const int token = tokens[row], pos = row_pos[row], first = seq_start[seq];
+    int prev = 0;
+    if (pos > 0) prev = row > first ? tokens[row - 1] : state[seq_slots[seq]];
+    __syncthreads();                                  // every thread has read the state before one of them writes it
+    if (row == first && threadIdx.x == 0) state[seq_slots[seq]] = tokens[first + seq_qlen[seq] - 1];
+    fr_pdl_launch();
+    const bool ok = token >= 0 && token < vocab;
+    const long long r = pos > 0 ? ((long long)prev * mul_prev + (long long)token * mul_cur) % (long long)buckets : (long long)buckets;
+    const TW* t = table + (size_t)(ok ? token : 0) * width;
+    const TW* b = pairs + (size_t)r * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = ok ? fr_load(t + i) + fr_load(b + i) : 0.f;
+}
+
+// ------------------------------------------------------------------ layer norm, then a short causal convolution added to it
+// h = layer_norm(x) rounded to the result's dtype; y_t = h_t + sum_j taps[:, j] * h_(t - n + 1 + j) (n taps; rows before the
+// sequence's start are zero).  Rows before a step's first come from the sequence's state: its last n - 1 rows h, oldest
+// first, 32-bit.  One block per row; the block norms the n - 1 rows before its own again instead of reading them from
+// memory that another block would have to write first.
+template <typename TO> __device__ __forceinline__ float round_as(float v);
+template <> __device__ __forceinline__ float round_as<float>(float v) { return v; }
+template <> __device__ __forceinline__ float round_as<bf16>(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+struct NormConvArgs {
+    const float* x;          // [rows][width]
+    FrVec w, b, taps;        // layer norm's weight and bias (b.p null: none); taps [width][n]
+    void* y;                 // [rows][width]
+    float* state;            // [slots][stride]: (n - 1) rows of width numbers at `offset`
+    long long stride, offset;
+    const int* row_seq;
+    const int* seq_start;
+    const int* seq_qlen;
+    const int* seq_slots;
+    int width, n, shift;     // shift: every sequence brings one row and the history moves on in the same kernel
+    float eps;
+};
+
+// mean and 1 / sqrt(variance + eps) of one row
+__device__ __forceinline__ void row_stats(const float* xr, int width, float eps, float* partial, float& mean, float& inv) {
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) sum += xr[i];
+    mean = block_sum(sum, partial) / (float)width;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float d = xr[i] - mean;
+        ss = fmaf(d, d, ss);
+    }
+    inv = 1.0f / sqrtf(block_sum(ss, partial) / (float)width + eps);
+}
+
+constexpr int CONV_MAX_TAPS = 8;
+
+template <typename TO>
+__global__ void __launch_bounds__(256) norm_conv_kernel(NormConvArgs p) {
+    __shared__ float partial[32];
+    __shared__ float stats[CONV_MAX_TAPS][2];
+    fr_pdl_wait();
+    fr_pdl_launch();
+    const int row = blockIdx.x, seq = p.row_seq[row];
+    TO* yr = (TO*)p.y + (size_t)row * p.width;
+    if (seq < 0) {
+        for (int i = threadIdx.x; i < p.width; i += blockDim.x) fr_store(yr + i, 0.f);
+        return;
+    }
+    const int t = row - p.seq_start[seq];               // rows of this sequence before this one in the step
+    float* hist = p.state + (size_t)p.seq_slots[seq] * p.stride + p.offset;
+    // statistics of the rows of the step that the taps reach: d rows back, d = 0 .. n - 1
+    for (int d = 0; d < p.n && d <= t; ++d) {
+        float mean, inv;
+        row_stats(p.x + (size_t)(row - d) * p.width, p.width, p.eps, partial, mean, inv);
+        if (threadIdx.x == 0) {
+            stats[d][0] = mean;
+            stats[d][1] = inv;
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < p.width; i += blockDim.x) {
+        const float wi = p.w.at(i), bi = p.b.p != nullptr ? p.b.at(i) : 0.f;
+        float acc = 0.f, own = 0.f, older[CONV_MAX_TAPS];
+        for (int d = p.n - 1; d >= 0; --d) {              // oldest first
+            float h;
+            if (d <= t) h = round_as<TO>((p.x[(size_t)(row - d) * p.width + i] - stats[d][0]) * stats[d][1] * wi + bi);
+            else h = hist[(size_t)(p.n - 1 - (d - t)) * p.width + i];       // d - t rows before the step's first
+            older[d] = h;
+            acc = fmaf(p.taps.at(i * p.n + (p.n - 1 - d)), h, acc);
+            if (d == 0) own = h;
+        }
+        fr_store(yr + i, own + acc);
+        if (p.shift)                                      // one row per sequence: the history takes it now
+            for (int k = 0; k + 1 < p.n; ++k) hist[(size_t)k * p.width + i] = older[p.n - 2 - k];
+    }
+}
+
+// After norm_conv: the history of every sequence takes the step's last n - 1 rows h (a step of fewer rows keeps the
+// youngest of what it had).  One block per sequence; a thread owns its channels, reads before it writes, and moves old rows
+// towards the front in rising order, so nothing is read after it was overwritten.
+template <typename TO>
+__global__ void __launch_bounds__(256) norm_conv_state_kernel(NormConvArgs p) {
+    __shared__ float partial[32];
+    fr_pdl_wait();
+    fr_pdl_launch();
+    const int seq = blockIdx.x, qlen = p.seq_qlen[seq], first = p.seq_start[seq];
+    if (qlen <= 0) return;
+    float* hist = p.state + (size_t)p.seq_slots[seq] * p.stride + p.offset;
+    for (int k = 0; k + 1 < p.n; ++k) {
+        const int s = qlen - (p.n - 1) + k;               // row of the step that becomes entry k; negative: an old entry
+        if (s < 0) {
+            for (int i = threadIdx.x; i < p.width; i += blockDim.x) hist[(size_t)k * p.width + i] = hist[(size_t)(k + qlen) * p.width + i];
+        } else {
+            float mean, inv;
+            const float* xr = p.x + (size_t)(first + s) * p.width;
+            row_stats(xr, p.width, p.eps, partial, mean, inv);
+            for (int i = threadIdx.x; i < p.width; i += blockDim.x)
+                hist[(size_t)k * p.width + i] = round_as<TO>((xr[i] - mean) * inv * p.w.at(i) + (p.b.p != nullptr ? p.b.at(i) : 0.f));
+        }
+    }
+}
+
+// out = x + half * (a / rms(a) * wa + b / rms(b) * wb): two results side by side, each normed over the width
+__global__ void __launch_bounds__(256)
+rms_pair_add_kernel(const float* __restrict__ x, const float* __restrict__ a, const float* __restrict__ b, FrVec wa, FrVec wb, float eps,
+                    float mult, float* __restrict__ out, int width) {
+    __shared__ float partial[32];
+    fr_pdl_wait();
+    fr_pdl_launch();
+    const size_t base = (size_t)blockIdx.x * width;
+    float sa = 0.f, sb = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float u = a[base + i], v = b[base + i];
+        sa = fmaf(u, u, sa);
+        sb = fmaf(v, v, sb);
+    }
+    const float ia = 1.0f / sqrtf(block_sum(sa, partial) / (float)width + eps);
+    const float ib = 1.0f / sqrtf(block_sum(sb, partial) / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+        out[base + i] = x[base + i] + mult * (a[base + i] * ia * wa.at(i) + b[base + i] * ib * wb.at(i));
+}
+
+}  // namespace
+
+FR_EXPORT int residual_embed_pair(const int* tokens, const int* row_seq, const int* row_pos, const int* seq_start, const int* seq_qlen,
+                                  const int* seq_slots, const void* table, const void* pairs, int table_dtype, int* state, float* out,
+                                  int n_rows, int width, int vocab, int buckets, long long mul_prev, long long mul_cur, cudaStream_t stream) {
+    if (n_rows <= 0) return FR_OK;
+    if (buckets <= 0) FR_REFUSE("embed_pair: %d buckets", buckets);
+    if (table_dtype == FR_F32)
+        FR_CUDA(fr_launch(embed_pair_kernel<float>, dim3(n_rows), dim3(256), 0, stream, tokens, row_seq, row_pos, seq_start, seq_qlen, seq_slots,
+                          (const float*)table, (const float*)pairs, state, out, width, vocab, buckets, mul_prev, mul_cur));
+    else if (table_dtype == FR_BF16)
+        FR_CUDA(fr_launch(embed_pair_kernel<bf16>, dim3(n_rows), dim3(256), 0, stream, tokens, row_seq, row_pos, seq_start, seq_qlen, seq_slots,
+                          (const bf16*)table, (const bf16*)pairs, state, out, width, vocab, buckets, mul_prev, mul_cur));
+    else FR_REFUSE("embed_pair: unknown dtype %d", table_dtype);
+    FR_CHECK_LAUNCH("embed_pair");
+    return FR_OK;
+}
+
+// x [rows][width] fp32 -> y in out_dtype; w, b (null: none) of w_dtype; taps [width][n] of taps_dtype; the history of a
+// sequence is (n - 1) * width floats at state + slot * stride + offset.  shift: every sequence brings exactly one row (the
+// history moves on in the kernel; otherwise call residual_norm_conv_state next).
+FR_EXPORT int residual_norm_conv(const float* x, const void* w, const void* b, int w_dtype, const void* taps, int taps_dtype, int n, void* y,
+                                 int out_dtype, float* state, long long stride, long long offset, const int* row_seq, const int* seq_start,
+                                 const int* seq_slots, int n_rows, int width, float eps, int shift, cudaStream_t stream) {
+    if (n_rows <= 0) return FR_OK;
+    if (n < 1 || n > CONV_MAX_TAPS) FR_REFUSE("norm_conv: %d taps (1 to %d)", n, CONV_MAX_TAPS);
+    NormConvArgs p;
+    p.x = x; p.w = FrVec{w, w_dtype}; p.b = FrVec{b, w_dtype}; p.taps = FrVec{taps, taps_dtype}; p.y = y; p.state = state; p.stride = stride;
+    p.offset = offset; p.row_seq = row_seq; p.seq_start = seq_start; p.seq_qlen = nullptr; p.seq_slots = seq_slots; p.width = width; p.n = n;
+    p.shift = shift && n > 1 ? 1 : 0; p.eps = eps;
+    if (out_dtype == FR_F32) FR_CUDA(fr_launch(norm_conv_kernel<float>, dim3(n_rows), dim3(256), 0, stream, p));
+    else if (out_dtype == FR_BF16) FR_CUDA(fr_launch(norm_conv_kernel<bf16>, dim3(n_rows), dim3(256), 0, stream, p));
+    else FR_REFUSE("norm_conv: unknown dtype %d", out_dtype);
+    FR_CHECK_LAUNCH("norm_conv");
+    return FR_OK;
+}
+
+FR_EXPORT int residual_norm_conv_state(const float* x, const void* w, const void* b, int w_dtype, int n, int out_dtype, float* state,
+                                       long long stride, long long offset, const int* seq_start, const int* seq_qlen, const int* seq_slots,
+                                       int n_seqs, int width, float eps, cudaStream_t stream) {
+    if (n_seqs <= 0 || n <= 1) return FR_OK;
+    if (n > CONV_MAX_TAPS) FR_REFUSE("norm_conv: %d taps (1 to %d)", n, CONV_MAX_TAPS);
+    NormConvArgs p;
+    p.x = x; p.w = FrVec{w, w_dtype}; p.b = FrVec{b, w_dtype}; p.taps = FrVec{nullptr, 0}; p.y = nullptr; p.state = state; p.stride = stride;
+    p.offset = offset; p.row_seq = nullptr; p.seq_start = seq_start; p.seq_qlen = seq_qlen; p.seq_slots = seq_slots; p.width = width; p.n = n;
+    p.shift = 0; p.eps = eps;
+    if (out_dtype == FR_F32) FR_CUDA(fr_launch(norm_conv_state_kernel<float>, dim3(n_seqs), dim3(256), 0, stream, p));
+    else if (out_dtype == FR_BF16) FR_CUDA(fr_launch(norm_conv_state_kernel<bf16>, dim3(n_seqs), dim3(256), 0, stream, p));
+    else FR_REFUSE("norm_conv: unknown dtype %d", out_dtype);
+    FR_CHECK_LAUNCH("norm_conv_state");
+    return FR_OK;
+}
+
+FR_EXPORT int residual_rms_pair_add(const float* x, const float* a, const float* b, const void* wa, const void* wb, int w_dtype, float eps,
+                                    float mult, float* out, int n_rows, int width, cudaStream_t stream) {
+    if (n_rows <= 0) return FR_OK;
+    FR_CUDA(fr_launch(rms_pair_add_kernel, dim3(n_rows), dim3(256), 0, stream, x, a, b, FrVec{wa, w_dtype}, FrVec{wb, w_dtype}, eps, mult, out, width));
+    FR_CHECK_LAUNCH("rms_pair_add");
+    return FR_OK;
+}

@@ -179,31 +179,39 @@ FR_EXPORT int rowwise_rmsnorm(const void* x, const void* w, int w_dtype, void* y
 // gu is [rows][2*inner] with gate and up interleaved: column 2f is gate f, column 2f+1 is up f (the rows of
 // the two projection matrices are stacked alternately, so that a product's tile holds both).
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inner, size_t total) {
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inner, size_t total, int act) {
     fr_pdl_wait();
     fr_pdl_launch();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
         const float g = fr_load(gu + 2 * idx);
         const float u = fr_load(gu + 2 * idx + 1);
-        fr_store(out + idx, g / (1.0f + expf(-g)) * u);
+        // act 2: the tanh form of gelu on the gate; otherwise silu
+        const float a = act == 2 ? 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) : g / (1.0f + expf(-g));
+        fr_store(out + idx, a * u);
     }
 }
 
-FR_EXPORT int rowwise_swiglu(const void* gu, void* out, int n_rows, int inner, int dtype, cudaStream_t stream) {
+// act 1: silu(gate) * up; act 2: gelu_tanh(gate) * up
+FR_EXPORT int rowwise_gated_act(const void* gu, void* out, int n_rows, int inner, int act, int dtype, cudaStream_t stream) {
     if (n_rows <= 0) return FR_OK;
+    if (act != 1 && act != 2) FR_REFUSE("gated activation: unknown kind %d", act);
     const size_t total = (size_t)n_rows * inner;
     const long long cap = (long long)(fr_sm_count() > 0 ? fr_sm_count() : 128) * 16;       // a few waves of the device
     const int blocks = (int)((long long)((total + 255) / 256) < cap ? (total + 255) / 256 : cap);
     if (dtype == FR_F32)
-        swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)out, inner, total);
+        swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)out, inner, total, act);
     else if (dtype == FR_BF16)
         FR_CUDA(fr_launch(swiglu_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)gu,
-                          (__nv_bfloat16*)out, inner, total));
+                          (__nv_bfloat16*)out, inner, total, act));
     else
         FR_REFUSE("swiglu: unknown dtype %d", dtype);
     FR_CHECK_LAUNCH("swiglu");
     return FR_OK;
+}
+
+FR_EXPORT int rowwise_swiglu(const void* gu, void* out, int n_rows, int inner, int dtype, cudaStream_t stream) {
+    return rowwise_gated_act(gu, out, n_rows, inner, 1, dtype, stream);
 }
 
 // ------------------------------------------------------------------ rotary + cache write

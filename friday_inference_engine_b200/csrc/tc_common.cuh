@@ -114,6 +114,11 @@ __device__ __forceinline__ float bias_at(const P& p, int i) {
 }
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
+// the gate's activation times up: act 1 silu, act 2 the tanh form of gelu
+__device__ __forceinline__ float gated_mul(int act, float g, float u) {
+    if (act == 2) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+    return silu_mul(g, u);
+}
 
 // Gated epilogue: rows 2f and 2f+1 of the weight are gate f and up f.  Must be called by whole warps.
 template <typename P>
@@ -123,7 +128,7 @@ __device__ __forceinline__ void finish16_gated(const P& p, int gi, int gj0, floa
         if (gi >= p.p_rows) return;
         float r[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) r[j] = silu_mul(v[2 * j], v[2 * j + 1]);
+        for (int j = 0; j < 8; ++j) r[j] = gated_mul(p.act, v[2 * j], v[2 * j + 1]);
         const int oj0 = gj0 >> 1, o_cols = p.q_rows >> 1;
         __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)gi * p.ldo + oj0;
         if (oj0 + 8 <= o_cols && (p.ldo % 8 == 0) && (((uintptr_t)p.out & 15) == 0)) {
@@ -142,7 +147,7 @@ __device__ __forceinline__ void finish16_gated(const P& p, int gi, int gj0, floa
         for (int j = 0; j < 16; ++j) up[j] = __shfl_xor_sync(0xffffffffu, v[j], 1);
         if ((gi & 1) || gi >= p.p_rows) return;
         for (int j = 0; j < 16 && gj0 + j < p.q_rows; ++j)
-            ((__nv_bfloat16*)p.out)[(size_t)(gj0 + j) * p.ldo + (gi >> 1)] = __float2bfloat16_rn(silu_mul(v[j], up[j]));
+            ((__nv_bfloat16*)p.out)[(size_t)(gj0 + j) * p.ldo + (gi >> 1)] = __float2bfloat16_rn(gated_mul(p.act, v[j], up[j]));
     }
 }
 

@@ -86,6 +86,9 @@ Json request_json(const CacheRequest& r) {
         j.set("window", Json(r.window));
         j.set("v_head_dim", Json(r.value_dim()));
         j.set("keep_first", Json(r.keep_first));
+        j.set("every", Json(r.every > 1 ? r.every : 1));
+        j.set("keys_only", Json(r.keys_only));
+        j.set("store_f32", Json(r.store_f32));
     } else if (r.kind == CacheRequest::Several) {
         Json parts = Json::array();
         for (const auto& p : r.parts) parts.push(request_json(p));
@@ -99,9 +102,14 @@ Json request_json(const CacheRequest& r) {
 
 CacheRequest request_from(const Json& j) {
     const std::string kind = j.get_string("kind", "none");
-    if (kind == "kv")
-        return CacheRequest::kv((int)j.get_int("n_kv_heads", 0), (int)j.get_int("head_dim", 0), (int)j.get_int("window", 0),
-                                (int)j.get_int("v_head_dim", 0), (int)j.get_int("keep_first", 0));
+    if (kind == "kv") {
+        CacheRequest r = CacheRequest::kv((int)j.get_int("n_kv_heads", 0), (int)j.get_int("head_dim", 0), (int)j.get_int("window", 0),
+                                          (int)j.get_int("v_head_dim", 0), (int)j.get_int("keep_first", 0));
+        r.every = (int)j.get_int("every", 1);
+        r.keys_only = j.get_bool("keys_only", false);
+        r.store_f32 = j.get_bool("store_f32", false);
+        return r;
+    }
     if (kind == "several") {
         std::vector<CacheRequest> parts;
         if (const Json* ps = j.find("parts"))

@@ -106,9 +106,7 @@ public:
         set_bound(bound_for(longest + 1));
         std::vector<const int*> tables;
         for (size_t g = 0; g < cache_.groups.size(); ++g) tables.push_back(buf_.as<int>() + table_off_[g]);
-        views_.clear();
-        for (const auto& call : model_.spec.program)
-            views_.push_back(call.cache < 0 ? CacheView() : cache_.view(call.cache, call.write, tables, seq_slots_));
+        views_ = cache_.program_views(model_.spec, tables, seq_slots_);
         ctx_ = StepContext();
         ctx_.rows = n_;
         ctx_.n_seqs = n_;

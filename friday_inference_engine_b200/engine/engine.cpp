@@ -181,9 +181,7 @@ size_t Stepper::step(const StepBatch& b, float* out, bool out_on_device) {
         ctx.seq_pos0 = dev + offs[6];
         std::vector<const int*> tables;
         for (size_t g = 0; g < n_groups; ++g) tables.push_back(dev + offs[8 + g]);
-        std::vector<CacheView> views;
-        for (const auto& call : model_.spec.program)
-            views.push_back(call.cache < 0 ? CacheView() : cache_.view(call.cache, call.write, tables, dev + offs[7]));
+        std::vector<CacheView> views = cache_.program_views(model_.spec, tables, dev + offs[7]);
 
         DecoderModel::RunOut r = model_.run(ops_, ctx, views, false, layer_arenas);
         if (nwant) {

@@ -59,6 +59,13 @@ DecoderModel::DecoderModel(const ModelSpec& s, DType dtype) : spec(s) {
             throw ConfigError("a learned position table is added to plain token rows of a 32-bit residual stream");
         root_->declare(spec.position_table, {spec.max_positions, spec.width});
     }
+    if (spec.has_embed_state()) {
+        const ModelSpec::PairTable& pt = spec.pair_table;
+        if (!spec.residual_f32 || !spec.embed_norm.kind.empty() || spec.embed_scale != 1.0 || !spec.position_table.empty())
+            throw ConfigError("a token-pair table is added to plain token rows of a 32-bit residual stream");
+        if (pt.buckets <= 0 || pt.mul_prev < 0 || pt.mul_cur < 0) throw ConfigError("a token-pair table needs positive 'buckets' and multipliers that are not negative");
+        root_->declare(pt.table, {pt.buckets + 1, spec.width});
+    }
     if (!spec.head.empty()) root_->declare(spec.head, {spec.vocab_size, spec.width});
     if (!spec.head_bias.empty()) root_->declare(spec.head_bias, {spec.vocab_size});
 }
@@ -75,6 +82,10 @@ std::vector<Part::Named> DecoderModel::named_params() {
 std::map<int, CacheRequest> DecoderModel::cache_requests() const {
     std::map<int, CacheRequest> out;
     for (const auto& kv : owners) out[kv.first] = layers[spec.program[kv.second].layer]->cache_request();
+    if (spec.has_embed_state()) {
+        if (out.count(ModelSpec::kEmbedStateEntry)) throw ConfigError("a program entry uses the cache entry that the embedding's state takes");
+        out[ModelSpec::kEmbedStateEntry] = CacheRequest::state({1}, DType::I32);      // the previous token
+    }
     return out;
 }
 
@@ -176,6 +187,7 @@ void DecoderModel::load(WeightSource& source, Ops& ops) {
     head = spec.head.empty() ? embedding : root_->tensor(spec.head);       // tied: one copy in memory
     if (!spec.head_bias.empty()) head_bias = root_->tensor(spec.head_bias);
     if (!spec.position_table.empty()) position_table = root_->tensor(spec.position_table);
+    if (spec.has_embed_state()) pair_table = root_->tensor(spec.pair_table.table);
     injections.clear();
     for (const auto& inj : spec.injections) injections.push_back(root_->tensor(inj.weight));
     std::map<std::string, Tensor> shared;
@@ -196,7 +208,11 @@ DecoderModel::RunOut DecoderModel::run(Ops& ops, const StepContext& ctx, const s
     values.arena = outer;
     StepContext with_values = ctx;
     with_values.values = &values;
-    if (position_table.defined()) {
+    if (pair_table.defined()) {
+        if (views.size() != spec.program.size() + 1) throw KernelError("the model's embedding keeps a state and was given no view of it");
+        const ModelSpec::PairTable& pt = spec.pair_table;
+        x = ops.embed_pair_rows(ctx, embedding, pair_table, pt.buckets, pt.mul_prev, pt.mul_cur, views.back());
+    } else if (position_table.defined()) {
         x = ops.embed_pos_rows(ctx, embedding, position_table);
     } else if (spec.residual_f32 && !embed_norm) {
         x = ops.embed_rows(ctx.tokens, ctx.rows, embedding, (float)spec.embed_scale);      // no rounding between table and stream

@@ -17,7 +17,9 @@
 // head size of their own (the value pool's rows are then that wide).  A request made of several
 // (a mixer that runs others side by side) is served part by part, each part as if it were an entry of its
 // own.  Every state request gets a tensor [slots, *shape]
-// that is zeroed when a slot is taken.  Lengths, not contents, decide what is valid:
+// that is zeroed when a slot is taken.  A request with `every` = P > 1 keeps one row for every P positions (a mixer's
+// pooled blocks): its group counts a sequence of n tokens as ceil(n / P) rows, has fewer pages accordingly and no window;
+// `store_f32` keeps its rows in 32-bit, `keys_only` leaves the value pool out.  Lengths, not contents, decide what is valid:
 // slots and pages are used again without being cleared.
 //
 // Capacity is given in tokens: `max_tokens` is the most that live sequences hold together,
@@ -61,6 +63,8 @@ class KVGroup {
 public:
     KVGroup(const CacheRequest& request, const std::vector<int>& entries, int n_slots, int n_pages, int width,
             DType dtype, bool on_device);
+    int every() const { return request.every > 1 ? request.every : 1; }
+    int rows_for(int tokens) const { return (tokens + every() - 1) / every(); }       // rows that `tokens` positions take
     CacheRequest request;
     std::vector<int> entries;        // cache entry ids, in pool order
     int window, n_pages, width;
@@ -71,7 +75,7 @@ public:
 
     int index_of(int entry) const;
     size_t entry_bytes() const { return (size_t)n_pages * PAGE * request.n_kv_heads * request.head_dim * dtype_size(dtype); }
-    size_t value_entry_bytes() const { return (size_t)n_pages * PAGE * request.n_kv_heads * request.value_dim() * dtype_size(dtype); }
+    size_t value_entry_bytes() const { return request.keys_only ? 0 : (size_t)n_pages * PAGE * request.n_kv_heads * request.value_dim() * dtype_size(dtype); }
     int kept_pages() const { return window > 0 ? (request.keep_first + PAGE - 1) / PAGE : 0; }    // never given back behind the window
     int first_needed_page(int start_pos) const;                     // logical page of the earliest key a query at start_pos or later sees
     std::vector<int> pages_missing(int slot, int start_pos, int new_len) const;
@@ -99,10 +103,16 @@ public:
     void table_rows(int g, const std::vector<int>& slots, std::vector<int>& out) const;
     // The view of `entry` for one layer call; tables: per group, this step's block table on the device.
     CacheView view(int entry, bool write, const std::vector<const int*>& step_tables, const int* seq_slots_dev) const;
+    // What DecoderModel::run takes: a view per program entry of `spec`, then the embedding's state if the model keeps one.
+    std::vector<CacheView> program_views(const ModelSpec& spec, const std::vector<const int*>& step_tables, const int* seq_slots_dev) const;
 
     int64_t held_tokens() const;
     size_t bytes() const;
-    int64_t capacity_tokens() const { return groups.empty() ? 0 : (int64_t)groups[0]->n_pages * PAGE; }
+    int64_t capacity_tokens() const {
+        for (const auto& g : groups)
+            if (g->every() == 1) return (int64_t)g->n_pages * PAGE;
+        return 0;
+    }
 
     int max_seq_tokens, max_slots;
     FreeList slots;

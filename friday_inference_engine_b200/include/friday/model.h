@@ -35,7 +35,7 @@ public:
     std::unique_ptr<Norm> final_norm, embed_norm;
     std::vector<Tensor> injections;               // the matrices of ModelSpec::injections
     std::map<int, int> owners;                     // cache entry -> program entry that writes it
-    Tensor embedding, head, head_bias, position_table;
+    Tensor embedding, head, head_bias, position_table, pair_table;
 
     // Every tensor the model needs, by full name (a layer that the run order names twice has its tensors once).
     std::vector<Part::Named> named_params();
@@ -52,7 +52,8 @@ public:
         bool has_normed = false;
         Rows normed;               // the final norm of every row, if asked for and produced on the way
     };
-    // views: one cache view per program entry.  Results of a layer live in one of two arenas in turn, so a layer's
+    // views: one cache view per program entry (and after them the embedding's state, if the model has one: Cache::program_views
+    // makes them).  Results of a layer live in one of two arenas in turn, so a layer's
     // working memory is taken back when the layer after the next starts; what must outlive the pass comes from
     // the arena that is current when run() is called.
     RunOut run(Ops& ops, const StepContext& ctx, const std::vector<CacheView>& views, bool with_final_norm,

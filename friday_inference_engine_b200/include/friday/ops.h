@@ -105,7 +105,8 @@ public:
     Tensor embedding(const int* tokens, int64_t n, const Tensor& table, Tensor* out = nullptr);
     Tensor gather_rows(const int* rows, int64_t n, const Tensor& src);
     Tensor rmsnorm(const Tensor& x, const Tensor& weight, float eps, Tensor* out = nullptr);
-    Tensor swiglu(const Tensor& gate_up);                     // columns alternate gate, up
+    // columns alternate gate, up; act 1: silu(gate) * up, act 2: gelu_tanh(gate) * up
+    Tensor swiglu(const Tensor& gate_up, int act = 1);
     // Rotates q and k inside qkv [rows, (nq + 2 nkv) * hd] (denominators null: no rotation) and, if the view
     // may be written, stores k and v in the cache rows of (row_seq, row_pos).
     void rope_kv_write(Tensor& qkv, const int* row_seq, const int* row_pos, const float* denominators, int rotary_dim,
@@ -149,6 +150,19 @@ public:
     void token_input(Tensor& x, const StepContext& ctx, const Tensor& table, int64_t col0, const Tensor& gate, const Tensor& proj,
                      const Tensor& norm, float eps);
 
+    // table[token] + pairs[(previous token * mul_prev + token * mul_cur) mod buckets] as 32-bit rows, the table's last row
+    // (number `buckets`) for a sequence's first token; the token before a step's first row comes from `view` (a state of one
+    // int32 per sequence), which then keeps the step's last token
+    Tensor embed_pair_rows(const StepContext& ctx, const Tensor& table, const Tensor& pairs, int64_t buckets, int64_t mul_prev,
+                           int64_t mul_cur, const CacheView& view);
+    // h + conv(h) with h = layer_norm(x) (bias null: none) in `out_dtype` and conv(h)_t = sum_j taps[:, j] h_(t - n + 1 + j) for
+    // taps [width, n], zeros before a sequence's start; `view` is a state of (n - 1) * width floats per sequence: its last
+    // n - 1 rows h, which the step's last rows replace
+    Tensor norm_conv(const Tensor& x, const Tensor& weight, const Tensor* bias, float eps, const Tensor& taps, const CacheView& view,
+                     const StepContext& ctx, DType out_dtype);
+    // x + mult * (a / rms(a) * wa + b / rms(b) * wb), all rows 32-bit: two results side by side, each normed over the width
+    Tensor rms_pair_add(const Tensor& x, const Tensor& a, const Tensor& b, const Tensor& wa, const Tensor& wb, float eps, float mult);
+
     // ---- mixers with a matrix state per head (csrc/recurrence.cu)
     // out [n][rows, width]: row + (row before - row) * mu[s]; the row before a step's first comes from the state
     Tensor shift_mix(const Tensor& h, const std::vector<Tensor>& mu, const CacheView& view, const StepContext& ctx);
@@ -184,6 +198,41 @@ public:
     // dt_bias [heads (* dk)]: beta = sigmoid(b_raw), decay = exp(-exp(a_log) * softplus(a_raw + dt_bias)); out [rows, heads * dv] fp32
     Tensor delta_scan(const Tensor& qkv, const Tensor& a_raw, const Tensor& b_raw, const Tensor& a_log, const Tensor& dt_bias,
                       const DeltaSpec& spec, const CacheView& view, const StepContext& ctx);
+
+    // The generalized delta rule: S <- diag(w) S - (a u)(u^T S) + k v^T with both terms reading the old state, o = S^T r;
+    // u = k / sqrt(sum k^2 + unit_eps) per head, w = exp(-rate * sigmoid(z + z_bias)), a = sigmoid(a_raw + a_bias).
+    // proj [rows, >= ...] holds r, k (heads * dk each) and v (heads * dv) at the given columns; z, a_raw [rows, heads * dk] fp32;
+    // view: a state of heads * dk * dv floats per sequence.  -> [rows, heads * dv] fp32
+    struct GeneralDeltaSpec {
+        int heads = 0, dk = 0, dv = 0;
+        float rate = 1.f, unit_eps = 1e-6f;
+        int64_t r_off = 0, k_off = 0, v_off = 0;
+    };
+    Tensor general_delta(const Tensor& proj, const Tensor& z, const Tensor& a_raw, const Tensor& z_bias, const Tensor& a_bias,
+                         const GeneralDeltaSpec& spec, const CacheView& view, const StepContext& ctx);
+
+    // ---- attention behind a window with pooled blocks, a sink, a query multiplier (csrc/attention_pooled.cu)
+    struct PooledSpec {
+        int heads = 0, kv_heads = 0, dim = 0, vdim = 0;
+        int window = 0;                 // 0: every earlier token is seen
+        int pool = 0;                   // > 0: blocks of this many tokens that lie wholly before the window are seen as one key and value
+        float scale = 1.f;
+        float temp_coef = 0.f;          // scores of the row at position p are multiplied by 1 + coef * ln(floor((p + 1) / every) + 1)
+        int temp_every = 0;             // 0: no such multiplier
+        const Tensor* sink = nullptr;   // [heads]: exp(sink_h) joins head h's denominator
+        const Tensor* q_norm = nullptr; // [dim]: RMS norm of every query head with this weight (null: none)
+        const Tensor* k_norm = nullptr;
+        float eps = 1e-5f;
+        const float* freq = nullptr;    // device [rot / 2]: pairs (i, i + rot / 2) of q and k turn by pos * freq[i]; null: no rotation
+        float rot_mult = 1.f;
+        int rot = 0;
+        int64_t q_off = 0, k_off = 0, v_off = -1;       // columns of the stacked projection; v_off < 0: the values are the keys
+    };
+    // q (normed, rotated) goes back into proj; k (normed, rotated) and v go to the cache rows of the step's tokens; with
+    // pooled blocks the blocks' sums (`pooled`: a view of 32-bit rows, one per `pool` positions) take the step's tokens
+    void pooled_store(Tensor& proj, const PooledSpec& spec, const CacheView& tokens, const CacheView* pooled, const StepContext& ctx);
+    // -> [rows, heads * vdim] in proj's dtype
+    Tensor pooled_attention(const Tensor& proj, const PooledSpec& spec, const CacheView& tokens, const CacheView* pooled, const StepContext& ctx);
 
     // ---- attention over a cached latent (csrc/attention_latent.cu)
     struct LatentSpec {
@@ -242,7 +291,8 @@ public:
                           const int* row_pos, const float* denominators, int rotary_dim, int n_heads, int n_kv_heads,
                           int head_dim, const CacheView* view);
     // silu(x Wg^T) * (x Wu^T) for weight_pairs [2 * inner, k] whose rows alternate gate, up.
-    Tensor linear_swiglu(const Rows& x, const Tensor& weight_pairs);
+    // act 2: the tanh form of gelu instead of silu
+    Tensor linear_swiglu(const Rows& x, const Tensor& weight_pairs, int act = 1);
     Tensor materialize(const Rows& h);
 
     // ---- attention of the step's rows over the paged cache.  q: the buffer that holds the queries, row stride

@@ -90,6 +90,13 @@ struct ModelSpec {
     // tensor name of a learned position table [max_positions, width] whose row of the token's position is added to the
     // token's row (32-bit stream, not scaled); empty: none
     std::string position_table;
+    // A hashed table of token pairs beside the token table (32-bit stream, no embedding norm): row
+    // (previous token * mul_prev + token * mul_cur) mod buckets of the tensor `table` [buckets + 1, width] is added to the
+    // token's row, the last row for a sequence's first token.  The previous token is kept per sequence by the cache.
+    struct PairTable {
+        std::string table;                      // empty: none
+        int64_t buckets = 0, mul_prev = 0, mul_cur = 0;
+    } pair_table;
     std::vector<PartSpec> layers;               // category "block"
     std::vector<LayerCall> program;
     PartSpec embed_norm;                        // kind empty: none; a norm applied to the token rows
@@ -111,6 +118,10 @@ struct ModelSpec {
 
     // cache entry -> index of the program entry that writes it; checks the program.
     std::map<int, int> cache_entries() const;
+    // The cache entry of what the embedding keeps per sequence (the previous token of a pair table); program entries use
+    // smaller numbers.  A model that has it gets its view as one more after the program entries' views.
+    static constexpr int kEmbedStateEntry = (1 << 20) - 1;
+    bool has_embed_state() const { return !pair_table.table.empty(); }
 };
 
 // ---- what a mixer may ask of the cache
@@ -119,12 +130,21 @@ struct CacheRequest {
     int n_kv_heads = 0, head_dim = 0, window = 0;    // KV: keys and values for every position, or the last `window`
     int v_head_dim = 0;                              // KV: size of a value head (0: the keys')
     int keep_first = 0;                              // KV with a window: positions below this stay visible (and held) for good
+    // KV: one row for every `every` positions instead of one per position (row r belongs to positions r * every ..
+    // r * every + every - 1: what a mixer keeps of blocks of tokens); such rows have no window
+    int every = 1;
+    bool keys_only = false;                          // KV: the values are the keys; no value pool (a view's v_pool is its k_pool)
+    bool store_f32 = false;                          // KV: 32-bit rows whatever the activations' dtype (sums that keep growing)
     std::vector<int64_t> state_shape;                // State: a tensor of this shape per sequence, zero at its start
     DType state_dtype = DType::F32;
     std::vector<CacheRequest> parts;                 // Several: what each of a mixer's sub-mixers asks for, in its order
     static CacheRequest kv(int n_kv_heads, int head_dim, int window = 0, int v_head_dim = 0, int keep_first = 0);
     static CacheRequest state(const std::vector<int64_t>& shape, DType dtype = DType::F32);
     static CacheRequest several(const std::vector<CacheRequest>& parts);
+    // several(...) with the parts of members that are themselves made of several spliced in (the cache serves one level)
+    static CacheRequest flat(const std::vector<CacheRequest>& members);
+    // how many parts `r` takes in flat(): its own parts if it is made of several, else one
+    static size_t flat_size(const CacheRequest& r) { return r.kind == Several ? r.parts.size() : 1; }
     int value_dim() const { return v_head_dim > 0 ? v_head_dim : head_dim; }
 };
 
@@ -139,12 +159,16 @@ struct CacheView {
     const int* block_table = nullptr;      // [n_seqs][table_width], -1 where the sequence holds no page
     int table_width = 0, page_size = 0, window = 0, n_kv_heads = 0, head_dim = 0;
     int v_head_dim = 0, keep_first = 0;    // values [pages][page_size][kv heads][v_head_dim]; see CacheRequest
+    int every = 1;                         // positions per row (CacheRequest::every)
     DType dtype = DType::F32;
     // State: state[slot] is the sequence's own tensor
     Tensor state;                          // [slots, ...]
     const int* seq_slots = nullptr;        // device: slot of every sequence of the step
     // Several: one view per part of the request
     std::vector<CacheView> parts;
+    // The view of a member whose request took `count` parts from part `first` on in CacheRequest::flat(): that part itself
+    // if the member's request was not made of several, else a view of several
+    CacheView member(size_t first, const CacheRequest& request) const;
 };
 
 // Rows that one layer of a pass leaves for later layers of the same pass (the values of a first attention layer that
@@ -242,6 +266,9 @@ public:
     // A norm of the form x / sqrt(mean(x^2) + eps) * weight answers with its parts whatever dtypes it reads and writes, so
     // that a block may run it inside a kernel that does more (a token shift after it, a residual sum before it).
     virtual bool rms_parts(Tensor* weight, float* eps) const { return false; }
+    // A layer norm (x - mean) / sqrt(variance + eps) * weight + bias answers with its parts (bias undefined: none), so that
+    // a block may run it inside a kernel that does more (a short convolution after it).
+    virtual bool layer_parts(Tensor* weight, Tensor* bias, float* eps) const { return false; }
 };
 
 class Position : public Part {
@@ -252,6 +279,8 @@ public:
     // A rotary encoding of neighbouring pairs: (2i, 2i + 1) of the first `dims` dimensions turn by pos * frequencies[i]
     // (a device table), cosine and sine multiplied by `multiplier`.  A mixer with a layout of its own hands these to its kernel.
     virtual bool pairs(const float** frequencies, float* multiplier, int* dims) const { return false; }
+    // The same table for pairs (i, i + dims / 2) among the first `dims` dimensions of a head.
+    virtual bool halves(const float** frequencies, float* multiplier, int* dims) const { return false; }
     // Any other encoding changes q and k inside qkv [rows, (n_heads + 2 n_kv_heads) * head_dim] itself.
     virtual void apply(Ops& ops, Tensor& qkv, const StepContext& ctx, int n_heads, int n_kv_heads, int head_dim) {}
 };

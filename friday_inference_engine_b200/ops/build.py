@@ -5,7 +5,7 @@ libfriday_engine.so holds everything between a model folder and its logits:
 configuration, weights, parts, cache, step function, decoder, generation loop.  It opens
 the kernel libraries itself, each when it is first needed; a kernel family (rowwise,
 gemm_simt, gemm_tc, attention_simt, attention_mma, attention_tc, attention_window, sampling, residual,
-recurrence, routed, delta, attention_latent, attention_talk) is one .cu
+recurrence, routed, delta, attention_latent, attention_talk, attention_pooled) is one .cu
 file with a C interface and becomes one .so beside it
 (friday_inference_engine_b200/_build/).  A library is compiled when it is first needed
 and was not made from the present sources, so a run compiles what its model and dtype
@@ -31,7 +31,7 @@ ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC,-fvisibility=hidden",
               "--expt-relaxed-constexpr"]
 FAMILIES = ("rowwise", "gemm_simt", "attention_simt", "sampling", "gemm_tc", "attention_mma", "attention_tc", "attention_window", "residual",
-            "recurrence", "routed", "delta", "attention_latent", "attention_talk")
+            "recurrence", "routed", "delta", "attention_latent", "attention_talk", "attention_pooled")
 PACKAGE = os.path.dirname(_HERE)
 SOURCE_DIRS = ("config", "weights", "parts", "cache", "engine", "sampling", "ops")
 INCLUDE = os.path.join(PACKAGE, "include")

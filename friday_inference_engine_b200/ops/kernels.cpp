@@ -91,6 +91,7 @@ std::string loaded_libraries() {
 FAMILY(Rowwise, rowwise, "rowwise",
        resolve(h, fam, "rowwise_embedding", t.embedding); resolve(h, fam, "rowwise_gather_rows", t.gather_rows);
        resolve(h, fam, "rowwise_rmsnorm", t.rmsnorm); resolve(h, fam, "rowwise_swiglu", t.swiglu);
+       resolve(h, fam, "rowwise_gated_act", t.gated_act);
        resolve(h, fam, "rowwise_rope_kv_write", t.rope_kv_write); resolve(h, fam, "rowwise_advance", t.advance);
        resolve(h, fam, "rowwise_scale_rows", t.scale_rows); resolve(h, fam, "rowwise_finish_logits", t.finish_logits);
        resolve(h, fam, "rowwise_random_normal", t.random_normal);)
@@ -106,7 +107,9 @@ FAMILY(Residual, residual, "residual", resolve(h, fam, "residual_norm_cast", t.n
        resolve(h, fam, "residual_gelu_table", t.gelu_table); resolve(h, fam, "residual_rms_add", t.rms_add);
        resolve(h, fam, "residual_layernorm_cast", t.layernorm_cast); resolve(h, fam, "residual_embed_rows", t.embed_rows);
        resolve(h, fam, "residual_embed_pos", t.embed_pos); resolve(h, fam, "residual_norm_shift", t.norm_shift);
-       resolve(h, fam, "residual_post_norm_add", t.post_norm_add); resolve(h, fam, "residual_two_sided_act", t.two_sided_act);)
+       resolve(h, fam, "residual_post_norm_add", t.post_norm_add); resolve(h, fam, "residual_two_sided_act", t.two_sided_act);
+       resolve(h, fam, "residual_embed_pair", t.embed_pair); resolve(h, fam, "residual_norm_conv", t.norm_conv);
+       resolve(h, fam, "residual_norm_conv_state", t.norm_conv_state); resolve(h, fam, "residual_rms_pair_add", t.rms_pair_add);)
 FAMILY(Recurrence, recurrence, "recurrence", resolve(h, fam, "recurrence_shift_mix", t.shift_mix);
        resolve(h, fam, "recurrence_tanh_rows", t.tanh_rows); resolve(h, fam, "recurrence_scan", t.scan);
        resolve(h, fam, "recurrence_scan_plan", t.scan_plan);
@@ -122,12 +125,17 @@ FAMILY(AttentionTalk, attention_talk, "attention_talk", resolve(h, fam, "attenti
        resolve(h, fam, "attention_talk_prompt_scratch_floats", t.prompt_scratch_floats);
        resolve(h, fam, "attention_talk_prompt", t.prompt);)
 FAMILY(Delta, delta, "delta", resolve(h, fam, "delta_conv_prepare", t.conv_prepare);
-       resolve(h, fam, "delta_conv_state", t.conv_state); resolve(h, fam, "delta_scan", t.scan);)
+       resolve(h, fam, "delta_conv_state", t.conv_state); resolve(h, fam, "delta_scan", t.scan);
+       resolve(h, fam, "delta_general_prepare", t.general_prepare); resolve(h, fam, "delta_general_scan", t.general_scan);)
 FAMILY(AttentionLatent, attention_latent, "attention_latent", resolve(h, fam, "attention_latent_rotate_pairs", t.rotate_pairs);
        resolve(h, fam, "attention_latent_prepare", t.prepare); resolve(h, fam, "attention_latent_head_linear", t.head_linear);
        resolve(h, fam, "attention_latent", t.run); resolve(h, fam, "attention_latent_gather", t.gather);
        resolve(h, fam, "attention_latent_softmax_split", t.softmax_split); resolve(h, fam, "attention_latent_gate_cast", t.gate_cast);
        resolve(h, fam, "attention_latent_key_concat", t.key_concat);)
+FAMILY(AttentionPooled, attention_pooled, "attention_pooled", resolve(h, fam, "attention_pooled_prepare", t.prepare);
+       resolve(h, fam, "attention_pooled_pool", t.pool); resolve(h, fam, "attention_pooled_scratch_floats", t.scratch_floats);
+       resolve(h, fam, "attention_pooled_rows", t.rows); resolve(h, fam, "attention_pooled_prompt_fits", t.prompt_fits);
+       resolve(h, fam, "attention_pooled_prompt", t.prompt);)
 FAMILY(AttentionMma, attention_mma, "attention_mma", resolve(h, fam, "attention_mma", t.run);
        resolve(h, fam, "attention_mma_clusters_at_once", t.clusters_at_once);)
 FAMILY(AttentionTc, attention_tc, "attention_tc", resolve(h, fam, "attention_tc", t.run);)

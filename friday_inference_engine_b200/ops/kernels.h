@@ -23,6 +23,7 @@ struct Rowwise {
     int (*gather_rows)(const int*, const void*, void*, int, int, int, cudaStream_t);
     int (*rmsnorm)(const void*, const void*, int, void*, int, int, float, int, cudaStream_t);
     int (*swiglu)(const void*, void*, int, int, int, cudaStream_t);
+    int (*gated_act)(const void*, void*, int, int, int, int, cudaStream_t);
     int (*rope_kv_write)(void*, const int*, const int*, const float*, int, int, int, int, void*, void*, const int*, int, int,
                          int, int, int, cudaStream_t);
     int (*advance)(int*, const int*, int*, int*, const int*, int*, int, cudaStream_t);
@@ -73,6 +74,13 @@ struct Residual {
     int (*post_norm_add)(const float*, const float*, const void*, int, float, float, float*, const void*, int, float, void*, int, int, int,
                          cudaStream_t);
     int (*two_sided_act)(void*, long long, int, const void*, int, cudaStream_t);
+    int (*embed_pair)(const int*, const int*, const int*, const int*, const int*, const int*, const void*, const void*, int, int*, float*, int,
+                      int, int, int, long long, long long, cudaStream_t);
+    int (*norm_conv)(const float*, const void*, const void*, int, const void*, int, int, void*, int, float*, long long, long long, const int*,
+                     const int*, const int*, int, int, float, int, cudaStream_t);
+    int (*norm_conv_state)(const float*, const void*, const void*, int, int, int, float*, long long, long long, const int*, const int*,
+                           const int*, int, int, float, cudaStream_t);
+    int (*rms_pair_add)(const float*, const float*, const float*, const void*, const void*, int, float, float, float*, int, int, cudaStream_t);
 };
 struct Recurrence {
     last_error_fn last_error;
@@ -94,6 +102,25 @@ struct Delta {
                       int, int, int, cudaStream_t);
     int (*scan)(const float*, const void*, int, const void*, int, int, const void*, const void*, int, float*, float*, long long,
                 long long, const int*, const int*, const int*, const int*, int, int, int, int, int, int, cudaStream_t);
+    int (*general_prepare)(const void*, int, int, int, const float*, int, const float*, int, const void*, const void*, int, float*, int, int,
+                           int, float, float, int, cudaStream_t);
+    int (*general_scan)(const float*, const void*, int, int, float*, float*, long long, long long, const int*, const int*, const int*, int,
+                        int, int, int, int, cudaStream_t);
+};
+struct AttentionPooled {
+    last_error_fn last_error;
+    int (*prepare)(void*, int, int, int, int, const void*, const void*, int, float, const float*, float, int, void*, void*, const int*, int,
+                   int, const int*, const int*, int, int, int, int, int, int, int, cudaStream_t);
+    int (*pool)(const void*, const void*, float*, float*, const int*, int, const int*, int, int, const int*, const int*, int, int, int, int,
+                int, int, int, cudaStream_t);
+    long long (*scratch_floats)(int, int, int, int);
+    int (*rows)(const void*, int, int, void*, const void*, const void*, const float*, const float*, const int*, int, const int*, int, int,
+                const int*, const int*, int, int, int, int, int, int, int, float, float, int, const void*, int, int, float*, int,
+                cudaStream_t);
+    int (*prompt_fits)(int, int, int);
+    int (*prompt)(const void*, int, int, void*, const void*, const void*, const float*, const float*, const int*, int, const int*, int, int,
+                  const int*, const int*, const int*, int, int, int, int, int, int, int, int, float, float, int, const void*, int,
+                  cudaStream_t);
 };
 struct AttentionLatent {
     last_error_fn last_error;
@@ -164,6 +191,7 @@ const Routed& routed();
 const Delta& delta();
 const AttentionLatent& attention_latent();
 const AttentionTalk& attention_talk();
+const AttentionPooled& attention_pooled();
 
 // Called with a family's name when its library is missing; returns 0 when it has built it.
 typedef int (*builder_fn)(const char* family);

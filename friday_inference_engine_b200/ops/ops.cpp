@@ -139,13 +139,13 @@ Tensor Ops::rmsnorm(const Tensor& x, const Tensor& weight, float eps, Tensor* ou
     return o;
 }
 
-Tensor Ops::swiglu(const Tensor& gate_up) {
+Tensor Ops::swiglu(const Tensor& gate_up, int act) {
     if (!gate_up.contiguous() || gate_up.cols() % 2) throw KernelError("swiglu: rows must be contiguous pairs (gate, up)");
     const int64_t inner = gate_up.cols() / 2;
     Tensor o = alloc(gate_up.dtype, gate_up.rows(), inner);
     const auto& k = kernels::rowwise();
     Timed t(*this, Other);
-    call(launches_, k, k.swiglu(gate_up.data, o.data, (int)gate_up.rows(), (int)inner, code(gate_up.dtype), stream_), "swiglu");
+    call(launches_, k, k.gated_act(gate_up.data, o.data, (int)gate_up.rows(), (int)inner, act, code(gate_up.dtype), stream_), "gated_act");
     return o;
 }
 
@@ -432,6 +432,138 @@ void Ops::token_input(Tensor& x, const StepContext& ctx, const Tensor& table, in
                                      gate.data, proj.data, norm.data, code(norm.dtype), (int)x.rows(), (int)x.cols(), (int)dim, eps, g,
                                      code(table.dtype), stream_), "token_input");
     ++launches_;
+}
+
+// ------------------------------------------------------------------ token pairs, the input convolution, two normed results
+Tensor Ops::embed_pair_rows(const StepContext& ctx, const Tensor& table, const Tensor& pairs, int64_t buckets, int64_t mul_prev,
+                            int64_t mul_cur, const CacheView& view) {
+    if (view.kind != CacheRequest::State || view.state.dtype != DType::I32 || !view.seq_slots)
+        throw KernelError("embed_pair_rows needs a state of one int32 per sequence");
+    if (pairs.dtype != table.dtype || pairs.cols() != table.cols() || pairs.rows() != buckets + 1)
+        throw KernelError("embed_pair_rows: the pair table has the token table's dtype and width and buckets + 1 rows");
+    Tensor o = alloc(DType::F32, ctx.rows, table.cols());
+    const auto& k = kernels::residual();
+    Timed t(*this, Other);
+    call(launches_, k, k.embed_pair(ctx.tokens, ctx.row_seq, ctx.row_pos, ctx.seq_start, ctx.seq_qlen, view.seq_slots, table.data, pairs.data,
+                                    code(table.dtype), (int*)view.state.data, (float*)o.data, ctx.rows, (int)table.cols(), (int)table.rows(),
+                                    (int)buckets, (long long)mul_prev, (long long)mul_cur, stream_), "embed_pair");
+    return o;
+}
+
+Tensor Ops::norm_conv(const Tensor& x, const Tensor& weight, const Tensor* bias, float eps, const Tensor& taps, const CacheView& view,
+                      const StepContext& ctx, DType out_dtype) {
+    const int64_t width = x.cols(), n = taps.cols();
+    if (x.dtype != DType::F32 || !x.contiguous() || weight.numel() != width || (bias && (bias->numel() != width || bias->dtype != weight.dtype)) ||
+        taps.rows() != width || !taps.contiguous())
+        throw KernelError("norm_conv: a contiguous 32-bit stream, a weight (and bias) of its width, taps [width, n]");
+    if (view.kind != CacheRequest::State || view.state.dtype != DType::F32 || view.state.numel() / view.state.shape[0] < (n - 1) * width)
+        throw KernelError("norm_conv needs a state of (taps - 1) * width floats per sequence");
+    const long long stride = view.state.numel() / view.state.shape[0];
+    Tensor o = alloc(out_dtype, x.rows(), width);
+    const auto& k = kernels::residual();
+    Timed t(*this, Other);
+    call(launches_, k, k.norm_conv((const float*)x.data, weight.data, bias ? bias->data : nullptr, code(weight.dtype), taps.data, code(taps.dtype),
+                                   (int)n, o.data, code(out_dtype), (float*)view.state.data, stride, 0, ctx.row_seq, ctx.seq_start, view.seq_slots,
+                                   (int)x.rows(), (int)width, eps, ctx.decode ? 1 : 0, stream_), "norm_conv");
+    if (!ctx.decode && n > 1)
+        call(launches_, k, k.norm_conv_state((const float*)x.data, weight.data, bias ? bias->data : nullptr, code(weight.dtype), (int)n,
+                                             code(out_dtype), (float*)view.state.data, stride, 0, ctx.seq_start, ctx.seq_qlen, view.seq_slots,
+                                             ctx.n_seqs, (int)width, eps, stream_), "norm_conv_state");
+    return o;
+}
+
+Tensor Ops::rms_pair_add(const Tensor& x, const Tensor& a, const Tensor& b, const Tensor& wa, const Tensor& wb, float eps, float mult) {
+    if (x.dtype != DType::F32 || a.dtype != DType::F32 || b.dtype != DType::F32 || !x.contiguous() || !a.contiguous() || !b.contiguous() ||
+        a.numel() != x.numel() || b.numel() != x.numel() || wa.numel() != x.cols() || wb.numel() != x.cols() || wa.dtype != wb.dtype)
+        throw KernelError("rms_pair_add: a contiguous 32-bit stream, two 32-bit addends of its size, two weights of its width");
+    Tensor o = alloc(DType::F32, x.rows(), x.cols());
+    const auto& k = kernels::residual();
+    Timed t(*this, Other);
+    call(launches_, k, k.rms_pair_add((const float*)x.data, (const float*)a.data, (const float*)b.data, wa.data, wb.data, code(wa.dtype), eps, mult,
+                                      (float*)o.data, (int)x.rows(), (int)x.cols(), stream_), "rms_pair_add");
+    return o;
+}
+
+// ------------------------------------------------------------------ the generalized delta rule
+Tensor Ops::general_delta(const Tensor& proj, const Tensor& z, const Tensor& a_raw, const Tensor& z_bias, const Tensor& a_bias,
+                          const GeneralDeltaSpec& s, const CacheView& view, const StepContext& ctx) {
+    const int64_t hk = (int64_t)s.heads * s.dk, hv = (int64_t)s.heads * s.dv;
+    if (z.dtype != DType::F32 || a_raw.dtype != DType::F32 || z.cols() < hk || a_raw.cols() < hk || z_bias.numel() != hk || a_bias.numel() != hk ||
+        z_bias.dtype != a_bias.dtype)
+        throw KernelError("general_delta: 32-bit decay and removal projections of heads * dk columns, biases of that size and one dtype");
+    if (view.kind != CacheRequest::State || view.state.dtype != DType::F32 || view.state.numel() / view.state.shape[0] < hk * s.dv)
+        throw KernelError("general_delta needs a state of heads * dk * dv floats per sequence");
+    const auto& k = kernels::delta();
+    float* prep = scratch_floats(proj.rows() * hk * 5);
+    Tensor o = alloc(DType::F32, proj.rows(), hv);
+    Timed t(*this, Other);
+    call(launches_, k, k.general_prepare(proj.data, (int)proj.ld, (int)s.r_off, (int)s.k_off, (const float*)z.data, (int)z.ld, (const float*)a_raw.data,
+                                         (int)a_raw.ld, z_bias.data, a_bias.data, code(z_bias.dtype), prep, (int)proj.rows(), s.heads, s.dk, s.rate,
+                                         s.unit_eps, code(proj.dtype), stream_), "general_prepare");
+    call(launches_, k, k.general_scan(prep, proj.data, (int)proj.ld, (int)s.v_off, (float*)o.data, (float*)view.state.data,
+                                      (long long)(view.state.numel() / view.state.shape[0]), 0, ctx.seq_start, ctx.seq_qlen, view.seq_slots, ctx.n_seqs,
+                                      s.heads, s.dk, s.dv, code(proj.dtype), stream_), "general_scan");
+    return o;
+}
+
+// ------------------------------------------------------------------ attention with pooled blocks, a sink, a query multiplier
+static void check_pooled(const Ops::PooledSpec& s, const CacheView& tokens, const CacheView* pooled, DType dtype) {
+    if (tokens.kind != CacheRequest::KV || !tokens.k_pool || tokens.dtype != dtype || tokens.n_kv_heads != s.kv_heads || tokens.head_dim != s.dim ||
+        (tokens.v_head_dim > 0 ? tokens.v_head_dim : tokens.head_dim) != s.vdim || tokens.every != 1)
+        throw KernelError("pooled attention: the cache view does not hold this mixer's keys and values in the rows' dtype");
+    if ((s.pool > 0) != (pooled != nullptr)) throw KernelError("pooled attention: pooled blocks and their cache view go together");
+    if (pooled && (pooled->kind != CacheRequest::KV || pooled->dtype != DType::F32 || pooled->every != s.pool || pooled->n_kv_heads != s.kv_heads ||
+                   pooled->head_dim != s.dim || (pooled->v_head_dim > 0 ? pooled->v_head_dim : pooled->head_dim) != s.vdim))
+        throw KernelError("pooled attention: the view of the pooled blocks must hold 32-bit rows of the keys' and values' sizes, one per block");
+    if (s.v_off < 0 && (tokens.v_pool != tokens.k_pool || s.vdim != s.dim)) throw KernelError("pooled attention: values that are the keys share the keys' pool");
+}
+
+void Ops::pooled_store(Tensor& proj, const PooledSpec& s, const CacheView& tokens, const CacheView* pooled, const StepContext& ctx) {
+    check_pooled(s, tokens, pooled, proj.dtype);
+    const auto& k = kernels::attention_pooled();
+    const int ndt = s.q_norm ? code(s.q_norm->dtype) : 0;
+    if (s.q_norm && s.k_norm && s.q_norm->dtype != s.k_norm->dtype) throw KernelError("pooled attention: the two norm weights have one dtype");
+    Timed t(*this, Other);
+    call(launches_, k, k.prepare(proj.data, (int)proj.ld, (int)s.q_off, (int)s.k_off, (int)(s.v_off < 0 ? 0 : s.v_off), s.q_norm ? s.q_norm->data : nullptr,
+                                 s.k_norm ? s.k_norm->data : nullptr, ndt, s.eps, s.freq, s.rot_mult, s.rot, tokens.k_pool,
+                                 s.v_off < 0 ? nullptr : tokens.v_pool, tokens.block_table, tokens.table_width, tokens.page_size, ctx.row_seq,
+                                 ctx.row_pos, (int)proj.rows(), s.heads, s.kv_heads, s.dim, s.vdim, tokens.write ? 1 : 0, code(proj.dtype), stream_),
+         "pooled prepare");
+    if (pooled && tokens.write)
+        call(launches_, k, k.pool(tokens.k_pool, tokens.v_pool, (float*)pooled->k_pool, (float*)pooled->v_pool, tokens.block_table, tokens.table_width,
+                                  pooled->block_table, pooled->table_width, tokens.page_size, ctx.seq_qlen, ctx.seq_pos0, ctx.n_seqs, ctx.max_q_len,
+                                  s.kv_heads, s.dim, s.vdim, s.pool, code(proj.dtype), stream_), "pooled pool");
+}
+
+Tensor Ops::pooled_attention(const Tensor& proj, const PooledSpec& s, const CacheView& tokens, const CacheView* pooled, const StepContext& ctx) {
+    check_pooled(s, tokens, pooled, proj.dtype);
+    const auto& k = kernels::attention_pooled();
+    Tensor out = alloc(proj.dtype, proj.rows(), (int64_t)s.heads * s.vdim);
+    const float* pk = pooled ? (const float*)pooled->k_pool : nullptr;
+    const float* pv = pooled ? (const float*)pooled->v_pool : nullptr;
+    const int* ptable = pooled ? pooled->block_table : nullptr;
+    const int pwidth = pooled ? pooled->table_width : 0;
+    const bool tc = proj.dtype == DType::BF16 && !ctx.decode && ctx.max_q_len >= 16 && env_on("FRIDAY_POOLED_TC") &&
+                    k.prompt_fits(s.dim, s.vdim, tokens.page_size) && ctx.n_seqs <= 65535;
+    Timed t(*this, Attention);
+    if (tc) {
+        call(launches_, k, k.prompt(proj.data, (int)proj.ld, (int)s.q_off, out.data, tokens.k_pool, tokens.v_pool, pk, pv, tokens.block_table,
+                                    tokens.table_width, ptable, pwidth, tokens.page_size, ctx.seq_start, ctx.seq_qlen, ctx.seq_pos0, ctx.n_seqs,
+                                    ctx.max_q_len, s.heads, s.kv_heads, s.dim, s.vdim, s.window, s.pool, s.scale, s.temp_coef, s.temp_every,
+                                    s.sink ? s.sink->data : nullptr, s.sink ? code(s.sink->dtype) : 0, stream_), "pooled prompt");
+        return out;
+    }
+    // keys that a row can face: its window (or everything before it) and the pooled blocks
+    int keys = ctx.max_kv_len;
+    if (s.window > 0) keys = std::min(keys, s.window + (s.pool > 0 ? ctx.max_kv_len / s.pool : 0));
+    const int splits = attention_splits(proj.rows(), s.heads, keys);
+    float* scratch = scratch_floats(k.scratch_floats((int)proj.rows(), s.heads, s.vdim, splits));
+    call(launches_, k, k.rows(proj.data, (int)proj.ld, (int)s.q_off, out.data, tokens.k_pool, tokens.v_pool, pk, pv, tokens.block_table,
+                              tokens.table_width, ptable, pwidth, tokens.page_size, ctx.row_seq, ctx.row_pos, (int)proj.rows(), s.heads, s.kv_heads,
+                              s.dim, s.vdim, s.window, s.pool, s.scale, s.temp_coef, s.temp_every, s.sink ? s.sink->data : nullptr,
+                              s.sink ? code(s.sink->dtype) : 0, splits, scratch, code(proj.dtype), stream_), "pooled rows");
+    ++launches_;                                     // the merge
+    return out;
 }
 
 // ------------------------------------------------------------------ mixers with a matrix state
@@ -944,7 +1076,7 @@ Tensor Ops::qkv_rope_write(const Rows& x, const Tensor& weight, const Tensor* bi
     return qkv;
 }
 
-Tensor Ops::linear_swiglu(const Rows& x, const Tensor& weight_pairs) {
+Tensor Ops::linear_swiglu(const Rows& x, const Tensor& weight_pairs, int act) {
     const Tensor& xt = x.t;
     check_product(xt, weight_pairs);
     const int64_t inner = weight_pairs.rows() / 2;
@@ -954,9 +1086,9 @@ Tensor Ops::linear_swiglu(const Rows& x, const Tensor& weight_pairs) {
         GemmFusion f;
         memset(&f, 0, sizeof f);
         fusion_in(x, f);
-        return linear_tc(xt, weight_pairs, nullptr, nullptr, out, -1, -1, -1, 1, x.deferred ? &f : nullptr);
+        return linear_tc(xt, weight_pairs, nullptr, nullptr, out, -1, -1, -1, act, x.deferred ? &f : nullptr);
     }
-    return swiglu(linear(x, weight_pairs));
+    return swiglu(linear(x, weight_pairs), act);
 }
 
 // ------------------------------------------------------------------ attention

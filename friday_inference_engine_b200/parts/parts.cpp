@@ -58,6 +58,33 @@ CacheRequest CacheRequest::several(const std::vector<CacheRequest>& parts) {
     return r;
 }
 
+CacheRequest CacheRequest::flat(const std::vector<CacheRequest>& members) {
+    CacheRequest r;
+    r.kind = Several;
+    for (const CacheRequest& m : members) {
+        if (m.kind != Several) {
+            r.parts.push_back(m);
+            continue;
+        }
+        for (const CacheRequest& p : m.parts) {
+            if (p.kind == Several) throw ConfigError("a cache request nests requests of several parts more than one level deep");
+            r.parts.push_back(p);
+        }
+    }
+    return r;
+}
+
+CacheView CacheView::member(size_t first, const CacheRequest& request) const {
+    const size_t count = CacheRequest::flat_size(request);
+    if (kind != CacheRequest::Several || first + count > parts.size()) throw KernelError("a cache view does not have the parts that its request was made of");
+    if (request.kind != CacheRequest::Several) return parts[first];
+    CacheView v;
+    v.kind = CacheRequest::Several;
+    v.write = write;
+    v.parts.assign(parts.begin() + (long)first, parts.begin() + (long)(first + count));
+    return v;
+}
+
 CacheRequest CacheRequest::state(const std::vector<int64_t>& shape, DType dtype) {
     CacheRequest r;
     r.kind = State;
@@ -215,6 +242,12 @@ public:
     Tensor forward(Ops& ops, const Tensor& x) override {
         return ops.layernorm_to(x, tensor(name_), has_bias_ ? &tensor(bias_name_) : nullptr, eps_, env.dtype);
     }
+    bool layer_parts(Tensor* weight, Tensor* bias, float* eps) const override {
+        *weight = tensor(name_);
+        *bias = has_bias_ ? tensor(bias_name_) : Tensor();
+        *eps = eps_;
+        return true;
+    }
 
 private:
     float eps_;
@@ -283,6 +316,10 @@ public:
     RotaryPairs(const PartSpec& s, const BuildEnv& e) : Position(e) {
         const double base = s.params.get_double("base", 0);
         dims_ = (int)s.params.get_int("dims", 0);
+        // "layout": "neighbours" pairs (2i, 2i + 1); "halves" pairs (i, i + dims / 2); the table is the same
+        const std::string layout = s.params.get_string("layout", "neighbours");
+        if (layout != "neighbours" && layout != "halves") throw ConfigError("rotary_pairs: 'layout' is \"neighbours\" or \"halves\"");
+        halves_ = layout == "halves";
         if (base <= 1.0) throw ConfigError("rotary_pairs: 'base' must be greater than 1");
         if (dims_ <= 0 || dims_ % 2) throw ConfigError(format("rotary_pairs: 'dims' = %d must be even and positive", dims_));
         const int half = dims_ / 2;
@@ -316,19 +353,30 @@ public:
         hold(mem);
     }
     bool pairs(const float** frequencies, float* multiplier, int* dims) const override {
+        if (halves_) return false;
         *frequencies = freq_;
         *multiplier = mult_;
         *dims = dims_;
         return true;
     }
+    bool halves(const float** frequencies, float* multiplier, int* dims) const override {
+        if (!halves_) return false;
+        *frequencies = freq_;
+        *multiplier = mult_;
+        *dims = dims_;
+        return true;
+    }
+    const std::vector<float>& table() const { return table_; }
     // inside a stacked q/k/v buffer: every query and key head's first `dims` dimensions
     void apply(Ops& ops, Tensor& qkv, const StepContext& ctx, int n_heads, int n_kv_heads, int head_dim) override {
+        if (halves_) throw ConfigError("rotary_pairs: the halves layout is applied by the mixers that ask for it, not inside a stacked q/k/v buffer");
         if (dims_ > head_dim) throw ConfigError(format("rotary_pairs: %d rotated dimensions in heads of %d", dims_, head_dim));
         ops.rotate_pairs(qkv, ctx, freq_, mult_, n_heads + n_kv_heads, head_dim, 0, dims_);
     }
 
 private:
     int dims_;
+    bool halves_ = false;
     float mult_ = 1.0f;
     std::vector<float> table_;
     const float* freq_ = nullptr;
@@ -537,13 +585,17 @@ public:
             return names && names->is_object() && names->has(role) ? names->at(role).as_string() : std::string(fallback);
         };
         down_ = name_of("down", "down_proj.weight");
+        // "activation" of the gate: "silu" (default) or "gelu_tanh"
+        const std::string act = s.params.get_string("activation", "silu");
+        if (act != "silu" && act != "gelu_tanh") throw ConfigError("swiglu: activation '" + act + "' is not one it has (silu, gelu_tanh)");
+        act_ = act == "gelu_tanh" ? 2 : 1;
         declare_stacked("w_gate_up", 2 * inner_, e.width);
         declare(name_of("gate", "gate_proj.weight"), {inner_, e.width}).stack("w_gate_up", 0, 2);
         declare(name_of("up", "up_proj.weight"), {inner_, e.width}).stack("w_gate_up", 1, 2);
         declare(down_, {e.width, inner_});
     }
     PartOut forward(Ops& ops, const Rows& h, const Tensor& residual, const StepContext&, Norm* then) override {
-        Tensor inner = ops.linear_swiglu(h, tensor("w_gate_up"));
+        Tensor inner = ops.linear_swiglu(h, tensor("w_gate_up"), act_);
         Tensor nw;
         float eps;
         if (then && residual.dtype == inner.dtype && then->as_rmsnorm(&nw, &eps)) {
@@ -556,6 +608,7 @@ public:
 
 private:
     int64_t inner_;
+    int act_ = 1;
     std::string down_;
 };
 
@@ -581,12 +634,34 @@ public:
             const PartSpec& ti = s.part("token_input");
             token_input_ = adopt(ti.prefix, build<TokenInput>("token_input", ti, e));
         }
+        // "input_conv": {"taps": n, "mixer": name, "feed_forward": name}: what each sublayer reads, h = norm(x), becomes
+        // h + conv(h), a causal convolution over time on each channel with the tensor [width, n] of that name (no bias),
+        // zeros before a sequence's start; the last n - 1 rows h of each sublayer are kept per sequence beside what the mixer
+        // asks of the cache.  The norms are layer norms; norm and convolution run as one kernel.
+        const Json* ic = s.params.find("input_conv");
+        if (ic && ic->is_object()) {
+            taps_ = (int)ic->get_int("taps", 0);
+            if (taps_ < 1 || taps_ > 8) throw ConfigError("prenorm block: 'input_conv' needs 1 to 8 'taps'");
+            conv1_ = ic->get_string("mixer", "");
+            conv2_ = ffn_ ? ic->get_string("feed_forward", "") : "";
+            if (conv1_.empty() || (ffn_ && conv2_.empty())) throw ConfigError("prenorm block: 'input_conv' names a tensor for every sublayer");
+            declare(conv1_, {e.width, (int64_t)taps_});
+            if (ffn_) declare(conv2_, {e.width, (int64_t)taps_});
+        }
     }
-    CacheRequest cache_request() const override { return mixer_->cache_request(); }
-    Norm* first_norm() override { return norm1_; }
+    CacheRequest cache_request() const override {
+        if (taps_ == 0) return mixer_->cache_request();
+        std::vector<CacheRequest> all{mixer_->cache_request()};
+        const int64_t hist = std::max<int64_t>(1, (int64_t)(taps_ - 1) * env.width);
+        all.push_back(CacheRequest::state({hist}, DType::F32));
+        if (ffn_) all.push_back(CacheRequest::state({hist}, DType::F32));
+        return CacheRequest::flat(all);
+    }
+    Norm* first_norm() override { return taps_ ? nullptr : norm1_; }        // with a convolution the norm runs inside this block
 
     PartOut forward(Ops& ops, const Tensor& x, const Rows* normed, const StepContext& ctx, const CacheView& view,
                     Norm* then) override {
+        if (taps_) return forward_conv(ops, x, ctx, view, then);
         Rows h = normed ? *normed : Rows(norm1_->forward(ops, x));
         Norm* after_last = token_input_ ? nullptr : then;       // a token input changes the stream after the last product
         PartOut b = mixer_->forward(ops, h, x, ctx, view, ffn_ ? norm2_ : after_last);
@@ -607,10 +682,40 @@ public:
     }
 
 private:
+    // the same block with h + conv(h) ahead of every sublayer
+    PartOut forward_conv(Ops& ops, const Tensor& x, const StepContext& ctx, const CacheView& view, Norm* then) {
+        if (x.dtype != DType::F32) throw ConfigError("prenorm block: an input convolution needs a 32-bit residual stream");
+        const CacheRequest mixer_request = mixer_->cache_request();
+        const size_t n_mixer = mixer_request.kind == CacheRequest::None ? 1 : CacheRequest::flat_size(mixer_request);
+        if (view.kind != CacheRequest::Several || view.parts.size() != n_mixer + (ffn_ ? 2 : 1))
+            throw KernelError("prenorm block: the cache view does not have the mixer's parts and the convolutions' histories");
+        Tensor w, b;
+        float eps = 0.f;
+        if (!norm1_->layer_parts(&w, &b, &eps)) throw ConfigError("prenorm block: an input convolution follows a layer norm");
+        Rows h(ops.norm_conv(x, w, b.defined() ? &b : nullptr, eps, tensor(conv1_), view.parts[n_mixer], ctx, env.dtype));
+        static const CacheView none;
+        PartOut out = mixer_->forward(ops, h, x, ctx, mixer_request.kind == CacheRequest::None ? none : view.member(0, mixer_request), nullptr);
+        if (ffn_) {
+            if (!norm2_->layer_parts(&w, &b, &eps)) throw ConfigError("prenorm block: an input convolution follows a layer norm");
+            Rows h2(ops.norm_conv(out.x, w, b.defined() ? &b : nullptr, eps, tensor(conv2_), view.parts[n_mixer + 1], ctx, env.dtype));
+            const Tensor mixed = out.x;
+            out = ffn_->forward(ops, h2, mixed, ctx, nullptr);
+        }
+        if (token_input_) token_input_->forward(ops, out.x, ctx);
+        out.has_normed = false;
+        if (then) {
+            out.normed = Rows(then->forward(ops, out.x));
+            out.has_normed = true;
+        }
+        return out;
+    }
+
     Norm *norm1_ = nullptr, *norm2_ = nullptr;
     Mixer* mixer_ = nullptr;
     FeedForward* ffn_ = nullptr;
     TokenInput* token_input_ = nullptr;
+    int taps_ = 0;
+    std::string conv1_, conv2_;
 };
 
 namespace {

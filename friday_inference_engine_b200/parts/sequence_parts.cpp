@@ -172,7 +172,10 @@ private:
 
 // ------------------------------------------------------------------ mixers side by side
 // out = residual + sum_i scale_i * member_i(h).  Members are named by the specification's "members" (roles of sub-parts,
-// in order) and weighted by "scales"; each keeps the part of the cache entry that it asked for.
+// in order) and weighted by "scales"; each keeps the part of the cache entry that it asked for (a member that asks for
+// several parts gets them as a view of several).  With "member_norms" (a tensor name [width] per member) every member's
+// result is first RMS-normed over the width with that weight ("eps"): out = residual + sum_i scale_i * norm_i(member_i(h));
+// the members then return their results alone, 32-bit, and the sum is one kernel for two members of equal scale.
 class ParallelMixer : public Mixer {
 public:
     ParallelMixer(const PartSpec& s, const BuildEnv& e) : Mixer(e) {
@@ -186,20 +189,55 @@ public:
             members_.push_back(adopt(ms.prefix, build<Mixer>("mixer", ms, e)));
             scales_.push_back((float)(*scales)[i].as_double());
         }
+        const Json* norms = s.params.find("member_norms");
+        if (norms && norms->is_array()) {
+            if (norms->size() != members->size()) throw ConfigError("parallel mixer: 'member_norms' names a tensor for every member");
+            eps_ = (float)s.params.get_double("eps", 1e-5);
+            for (size_t i = 0; i < norms->size(); ++i) {
+                norm_names_.push_back((*norms)[i].as_string());
+                declare(norm_names_.back(), {e.width}, false, true);
+            }
+        }
     }
     CacheRequest cache_request() const override {
         std::vector<CacheRequest> parts;
         for (const Mixer* m : members_) parts.push_back(m->cache_request());
-        return CacheRequest::several(parts);
+        return CacheRequest::flat(parts);
     }
     PartOut forward(Ops& ops, const Rows& h, const Tensor& residual, const StepContext& ctx, const CacheView& view, Norm*) override {
-        if (view.kind != CacheRequest::Several || view.parts.size() != members_.size())
+        std::vector<CacheView> views;
+        size_t at = 0;
+        for (const Mixer* m : members_) {
+            const CacheRequest r = m->cache_request();
+            if (r.kind == CacheRequest::None) {
+                views.emplace_back();
+                at += 1;
+                continue;
+            }
+            views.push_back(view.member(at, r));
+            at += CacheRequest::flat_size(r);
+        }
+        if (view.kind != CacheRequest::Several || view.parts.size() != at)
             throw KernelError("parallel mixer: the cache view does not have a part per member");
         Rows x(ops.materialize(h));
+        if (!norm_names_.empty()) {
+            if (!residual.defined() || residual.dtype != DType::F32) throw ConfigError("parallel mixer: normed members add into a 32-bit residual stream");
+            std::vector<Tensor> ys;
+            for (size_t i = 0; i < members_.size(); ++i) {
+                members_[i]->out_scale = 1.0f;
+                ys.push_back(members_[i]->forward(ops, x, Tensor(), ctx, views[i], nullptr).x);
+                if (ys.back().dtype != DType::F32) throw ConfigError("parallel mixer: a member handed no residual must return 32-bit rows");
+            }
+            if (members_.size() == 2 && scales_[0] == scales_[1])
+                return PartOut(ops.rms_pair_add(residual, ys[0], ys[1], tensor(norm_names_[0]), tensor(norm_names_[1]), eps_, out_scale * scales_[0]));
+            Tensor sum = residual;
+            for (size_t i = 0; i < members_.size(); ++i) sum = ops.post_norm_add(sum, ys[i], tensor(norm_names_[i]), eps_, out_scale * scales_[i]);
+            return PartOut(sum);
+        }
         Tensor sum = residual;
         for (size_t i = 0; i < members_.size(); ++i) {
             members_[i]->out_scale = out_scale * scales_[i];
-            sum = members_[i]->forward(ops, x, sum, ctx, view.parts[i], nullptr).x;
+            sum = members_[i]->forward(ops, x, sum, ctx, views[i], nullptr).x;
         }
         return PartOut(sum);
     }
@@ -207,6 +245,8 @@ public:
 private:
     std::vector<Mixer*> members_;
     std::vector<float> scales_;
+    std::vector<std::string> norm_names_;
+    float eps_ = 1e-5f;
 };
 
 // ------------------------------------------------------------------ routed experts
