@@ -13,11 +13,19 @@ from ..native import CacheError, CacheFull  # noqa: F401
 PAGE = 64
 
 
-def kv_request(n_kv_heads, head_dim, window=None, v_head_dim=None, keep_first=0):
+def kv_request(n_kv_heads, head_dim, window=None, v_head_dim=None, keep_first=0, every=1, keys_only=False, store_f32=False):
     """v_head_dim: size of a value head if it differs from the keys'; keep_first: behind a window, positions below this
-    stay visible, so their pages are held as long as the sequence lives."""
-    return {"kind": "kv", "n_kv_heads": int(n_kv_heads), "head_dim": int(head_dim), "window": int(window or 0),
-            "v_head_dim": int(v_head_dim or 0), "keep_first": int(keep_first)}
+    stay visible, so their pages are held as long as the sequence lives; every: one row for that many positions (a mixer's
+    pooled blocks); keys_only: no value pool; store_f32: 32-bit rows whatever the activations' dtype."""
+    r = {"kind": "kv", "n_kv_heads": int(n_kv_heads), "head_dim": int(head_dim), "window": int(window or 0),
+         "v_head_dim": int(v_head_dim or 0), "keep_first": int(keep_first)}
+    if every > 1:
+        r["every"] = int(every)
+    if keys_only:
+        r["keys_only"] = True
+    if store_f32:
+        r["store_f32"] = True
+    return r
 
 
 def several(*parts):

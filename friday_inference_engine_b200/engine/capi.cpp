@@ -86,9 +86,9 @@ Json request_json(const CacheRequest& r) {
         j.set("window", Json(r.window));
         j.set("v_head_dim", Json(r.value_dim()));
         j.set("keep_first", Json(r.keep_first));
-        j.set("every", Json(r.every > 1 ? r.every : 1));
-        j.set("keys_only", Json(r.keys_only));
-        j.set("store_f32", Json(r.store_f32));
+        if (r.every > 1) j.set("every", Json(r.every));              // what only some mixers ask for is named only then
+        if (r.keys_only) j.set("keys_only", Json(true));
+        if (r.store_f32) j.set("store_f32", Json(true));
     } else if (r.kind == CacheRequest::Several) {
         Json parts = Json::array();
         for (const auto& p : r.parts) parts.push(request_json(p));
