@@ -651,6 +651,52 @@ def beletar_numbers(cfg, batch, context, prompt_len):
     return {"step_bytes": weight_bytes + state_bytes + kv_bytes, "flops_per_token": flops}
 
 
+def vulanex_config(width, layers=7, vocab=32768, window=1024, pool=64):
+    """A Vulanex configuration whose layers have sizes like a real model's of this width: heads of 128 on a quarter as many
+    key/value heads; in the even layers causal attention whose values are its keys, in the odd ones attention behind a window
+    of `window` tokens with pooled blocks of `pool` beside the generalized delta rule with heads of 128 x 128; input
+    convolutions of four taps; a gated feed-forward of three times the width everywhere."""
+    heads, kv = max(1, width // 128), max(1, width // 512)
+    att = {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "q_temp": {"coef": 0.5, "every": 64}}
+    left = {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": window, "pool": pool},
+            "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    par = {"left": left, "right": {"heads": heads, "dim": 128, "decay_rank": 64}}
+    mlp = {"kind": "dense", "ff": 3 * width}
+    ls = [{"type": "attention" if i % 2 == 0 else "parallel", "mixer": att if i % 2 == 0 else par, "mlp": mlp} for i in range(layers)]
+    return {"architecture": "Vulanex", "vocab": vocab, "width": width, "logit_scale": 1.0, "norm": {"eps": 1e-5}, "canon": {"taps": 4},
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}}, "layers": ls}
+
+
+def vulanex_numbers(cfg, batch, context, prompt_len):
+    """What a decode step of `batch` sequences must read (weights, cached keys and values in sight, the blocks' sums, the
+    states) and what a prompt token costs (the attention's share for a prompt of prompt_len tokens)."""
+    w, v, taps = cfg["width"], cfg["vocab"], cfg["canon"]["taps"]
+    weight_bytes = 2 * v * w
+    state_bytes = kv_bytes = 0
+    flops = 2 * v * w
+    for L in cfg["layers"]:
+        m = L["mixer"]
+        if L["type"] == "attention":
+            H, G, d = m["heads"], m["kv_heads"], m["dim"]
+            mat = (H * d + G * d) * w + w * H * d
+            kv_bytes += batch * context * G * d * 2                       # keys only: they are the values
+            mix = 2 * H * 2 * d * prompt_len // 2
+        else:
+            l, r = m["left"], m["right"]
+            H, G, d, vd, size, P = l["heads"], l["kv_heads"], l["dim"], l["vdim"], l["mask"]["size"], l["mask"]["pool"]
+            hd = r["heads"] * r["dim"]
+            mat = (H * d + G * d + G * vd) * w + w * H * vd + 5 * hd * w + r["decay_rank"] * (w + hd) + w * hd
+            kv_bytes += batch * (min(context, size) * G * (d + vd) * 2 + max(0, context - size) // P * G * (d + vd) * 4)
+            state_bytes += batch * r["heads"] * r["dim"] * r["dim"] * 4 * 2
+            seen = sum(min(i + 1, size) + max(0, i - size + 1) // P for i in range(prompt_len)) / prompt_len
+            mix = 2 * H * (d + vd) * seen + 7 * r["heads"] * r["dim"] * r["dim"]
+        ff = 3 * L["mlp"]["ff"] * w if L.get("mlp") else 0
+        state_bytes += batch * (2 if L.get("mlp") else 1) * (taps - 1) * w * 4 * 2
+        weight_bytes += 2 * (mat + ff)
+        flops += 2 * (mat + ff) + mix
+    return {"step_bytes": weight_bytes + state_bytes + kv_bytes, "flops_per_token": flops}
+
+
 def tikunex_numbers(cfg, batch, context):
     """What a decode step of `batch` sequences must read and what a prompt token costs, per run of the layers."""
     w, v = cfg["width"], cfg["vocab"]
@@ -696,7 +742,7 @@ def tikunex_numbers(cfg, batch, context):
 
 
 def design_compare(Engine, args):
-    """Ditenex, Beletar and Tikunex beside the Qwen2.5 dense decoder at equal width and depth (random weights): one prompt and decode
+    """Vulanex, Ditenex, Beletar and Tikunex beside the Qwen2.5 dense decoder at equal width and depth (random weights): one prompt and decode
     steps, with the share of each kind of kernel in the prompt (event-bracketed).  One line of text per measurement.
     --designs picks among them."""
     pk = peaks()
@@ -704,6 +750,7 @@ def design_compare(Engine, args):
     for width in [int(v) for v in args.design_compare.split(",") if v]:
         layers = args.layers or 4
         designs = [
+            ("vulanex", vulanex_config(width, 2 * layers - 1)),
             ("ditenex", ditenex_config(width, 2 * layers - 1)),
             ("beletar", beletar_config(width, layers)),
             ("tikunex", tikunex_config(width, layers)),
@@ -714,7 +761,10 @@ def design_compare(Engine, args):
             if name not in args.designs.split(","):
                 continue
             eng = Engine(config=cfg, seed=0, dtype="bfloat16", max_ctx=4096, max_batch=batch, max_tokens=batch * 4096 + 8192)
-            if name == "ditenex":
+            if name == "vulanex":
+                nums = vulanex_numbers(cfg, batch, context + 64, prompt_len)
+                flops_tok, step_bytes = nums["flops_per_token"], nums["step_bytes"]
+            elif name == "ditenex":
                 nums = ditenex_numbers(cfg, batch, context + 64, prompt_len)
                 flops_tok, step_bytes = nums["flops_per_token"], nums["step_bytes"]
             elif name == "beletar":
@@ -784,9 +834,9 @@ def main():
     ap.add_argument("--prefill-chunk", type=int, default=0, dest="prefill_chunk",
                     help="most tokens of a sequence per pass in the sweeps (0: the engine's own)")
     ap.add_argument("--design-compare", default="", dest="design_compare",
-                    help="widths, e.g. 1024,2048,4096: a Ditenex, a Beletar and a Tikunex model with layers of that size beside the Qwen2.5 "
+                    help="widths, e.g. 1024,2048,4096: a Vulanex, a Ditenex, a Beletar and a Tikunex model with layers of that size beside the Qwen2.5 "
                          "decoder of equal width (prompt, decode steps, kernel shares): lines of text")
-    ap.add_argument("--designs", default="ditenex,beletar,tikunex,qwen2", help="which designs --design-compare runs")
+    ap.add_argument("--designs", default="vulanex,ditenex,beletar,tikunex,qwen2", help="which designs --design-compare runs")
     ap.add_argument("--timeline", action="store_true",
                     help="print the kernels of one decode step as they run inside the captured graph (torch profiler)")
     args = ap.parse_args()

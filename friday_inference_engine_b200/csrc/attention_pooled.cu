@@ -142,16 +142,26 @@ __global__ void __launch_bounds__(128) pool_kernel(PoolArgs p) {
     const size_t prow = (size_t)p.pool_table[(size_t)seq * p.pool_table_width + b / PAGE_ROWS] * PAGE_ROWS + b % PAGE_ROWS;
     const int* table = p.block_table + (size_t)seq * p.table_width;
     const int kc = p.kv_heads * p.dim, vc = p.kv_heads * p.vdim;
-    for (int c = threadIdx.x; c < kc + vc; c += blockDim.x) {
-        const bool key = c < kc;
-        float* dst = key ? p.pk_pool + prow * kc + c : p.pv_pool + prow * vc + (c - kc);
-        float acc = fresh ? 0.f : *dst;
-        for (int j = j0; j <= j1; ++j) {
-            const size_t at = (size_t)table[j / PAGE_ROWS] * PAGE_ROWS + j % PAGE_ROWS;
-            acc += key ? fr_load((const T*)p.k_pool + at * kc + c) : fr_load((const T*)p.v_pool + at * vc + (c - kc));
+    const int c = blockIdx.z * blockDim.x + threadIdx.x;       // a thread per channel of the keys, then of the values
+    if (c >= kc + vc) return;
+    const bool key = c < kc;
+    float* dst = key ? p.pk_pool + prow * kc + c : p.pv_pool + prow * vc + (c - kc);
+    const T* src = key ? (const T*)p.k_pool + c : (const T*)p.v_pool + (c - kc);
+    const int width = key ? kc : vc;
+    float acc = fresh ? 0.f : *dst;
+    // in the order of positions, four loads in flight
+    for (int j = j0; j <= j1; j += 4) {
+        float v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int ju = min(j + u, j1);
+            v[u] = fr_load(src + ((size_t)table[ju / PAGE_ROWS] * PAGE_ROWS + ju % PAGE_ROWS) * width);
         }
-        *dst = acc;
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (j + u <= j1) acc += v[u];
     }
+    *dst = acc;
 }
 
 // ------------------------------------------------------------------ rows (CUDA cores)
@@ -608,7 +618,8 @@ FR_EXPORT int attention_pooled_pool(const void* k_pool, const void* v_pool, floa
     p.k_pool = k_pool; p.v_pool = v_pool; p.pk_pool = pk_pool; p.pv_pool = pv_pool; p.block_table = block_table; p.pool_table = pool_table;
     p.seq_qlen = seq_qlen; p.seq_pos0 = seq_pos0; p.table_width = table_width; p.pool_table_width = pool_table_width; p.kv_heads = kv_heads;
     p.dim = dim; p.vdim = vdim; p.pool = pool;
-    const dim3 grid(n_seqs, (max_q_len + pool - 1) / pool + 1);
+    const dim3 grid(n_seqs, (max_q_len + pool - 1) / pool + 1, (kv_heads * (dim + vdim) + 127) / 128);
+    if (grid.y > 65535 || grid.z > 65535) FR_REFUSE("attention_pooled: %d blocks of tokens in a step, %d channels", (int)grid.y, kv_heads * (dim + vdim));
     if (dtype == FR_F32) FR_CUDA(fr_launch(pool_kernel<float>, grid, dim3(128), 0, stream, p));
     else if (dtype == FR_BF16) FR_CUDA(fr_launch(pool_kernel<bf16>, grid, dim3(128), 0, stream, p));
     else FR_REFUSE("attention_pooled: unknown dtype %d", dtype);

@@ -537,16 +537,19 @@ struct GeneralScanArgs {
 };
 
 // tokens staged at a time: fewer where a token is wide, so that what a thread holds of the next chunk stays in registers
-constexpr int gen_tokens(int dkp) { return dkp <= 64 ? 8 : (dkp <= 128 ? 4 : 2); }
+constexpr int gen_tokens(int dkp, int lpc) { return lpc >= 16 ? (dkp <= 128 ? 8 : 4) : (dkp <= 64 ? 8 : (dkp <= 128 ? 4 : 2)); }
 
-// DKP: key channels rounded up to 16, 32, 64, 128 or 256; a lane holds DKP / 4 of them, dealt out in groups of four so that
-// the four lanes of a column read neighbouring 16-byte pieces of shared memory
-template <typename T, int DKP>
+// DKP: key channels rounded up to 16, 32, 64, 128 or 256.  LPC lanes share a value channel (a column of S): 4, or 16 where
+// the step has few sequences (a lane's share of a token is then a quarter as long, and four times as many warps fill the
+// device); a lane holds DKP / LPC key channels, dealt out in groups of four so that the lanes of a column read neighbouring
+// 16-byte pieces of shared memory.
+template <typename T, int DKP, int LPC>
 __global__ void __launch_bounds__(128) general_scan_kernel(GeneralScanArgs p) {
     extern __shared__ __align__(16) float gsm[];
-    constexpr int PER = DKP / 4, VEC = 5 * DKP, GEN_TOKENS = gen_tokens(DKP);
-    const int seq = blockIdx.x, head = blockIdx.y, tid = threadIdx.x, threads = blockDim.x;
-    const int part = tid & 3, local_col = tid >> 2, col = blockIdx.z * p.cols + local_col;
+    constexpr int PER = DKP / LPC, VEC = 5 * DKP, GEN_TOKENS = gen_tokens(DKP, LPC), COLS = 128 / LPC;
+    static_assert(PER >= 4 && PER % 4 == 0, "a lane holds whole groups of four key channels");
+    const int seq = blockIdx.x, head = blockIdx.y, tid = threadIdx.x;
+    const int part = tid % LPC, local_col = tid / LPC, col = blockIdx.z * p.cols + local_col;
     const bool live_col = local_col < p.cols && col < p.dv;
     fr_pdl_wait();
     fr_pdl_launch();
@@ -556,51 +559,53 @@ __global__ void __launch_bounds__(128) general_scan_kernel(GeneralScanArgs p) {
     float s[PER];
 #pragma unroll
     for (int j = 0; j < PER; ++j) {
-        const int i = 4 * (4 * (j >> 2) + part) + (j & 3);
+        const int i = 4 * (LPC * (j >> 2) + part) + (j & 3);
         s[j] = (live_col && i < p.dk) ? S[(size_t)i * p.dv + col] : 0.f;
     }
-    const int buf_floats = GEN_TOKENS * (VEC + p.cols);
+    constexpr int BUF = GEN_TOKENS * (VEC + COLS);
     // what one thread loads of a chunk: vectors (w, a u, u, k, r padded to DKP with zeros) and the block's value channels
-    constexpr int N_IT = (GEN_TOKENS * VEC + 127) / 128;
-    const int n_v = (GEN_TOKENS * p.cols + threads - 1) / threads;          // at most 2 with 32 columns and 128 threads
-    float held[N_IT], held_v[2];
+    constexpr int N_IT = (GEN_TOKENS * VEC + 127) / 128, N_V = (GEN_TOKENS * COLS + 127) / 128;
+    float held[N_IT], held_v[N_V];
+    const float* prep = p.prep + ((size_t)r0 * p.heads + head) * 5 * p.dk;
+    const T* vals = (const T*)p.v + (size_t)r0 * p.ld_v + p.v_off + head * p.dv + blockIdx.z * p.cols;
     auto fetch = [&](int t0) {
         const int nt = min(GEN_TOKENS, n - t0);
 #pragma unroll
         for (int it = 0; it < N_IT; ++it) {
-            const int idx = tid + it * threads;
+            const int idx = tid + it * 128;
             const int t = idx / VEC, rest = idx - t * VEC, which = rest / DKP, i = rest - which * DKP;
-            held[it] = (idx < GEN_TOKENS * VEC && t < nt && i < p.dk)
-                           ? p.prep[((size_t)(r0 + t0 + t) * p.heads + head) * 5 * p.dk + (size_t)which * p.dk + i] : 0.f;
+            held[it] = (idx < GEN_TOKENS * VEC && t < nt && i < p.dk) ? prep[(size_t)(t0 + t) * p.heads * 5 * p.dk + which * p.dk + i] : 0.f;
         }
-        for (int it = 0; it < n_v && it < 2; ++it) {
-            const int idx = tid + it * threads;
-            const int t = idx / p.cols, c = idx - t * p.cols;
-            const int cc = blockIdx.z * p.cols + c;
-            held_v[it] = (idx < GEN_TOKENS * p.cols && t < nt && cc < p.dv)
-                             ? fr_load((const T*)p.v + (size_t)(r0 + t0 + t) * p.ld_v + p.v_off + head * p.dv + cc) : 0.f;
+#pragma unroll
+        for (int it = 0; it < N_V; ++it) {
+            const int idx = tid + it * 128;
+            const int t = idx / COLS, c = idx - t * COLS;
+            held_v[it] = (idx < GEN_TOKENS * COLS && t < nt && c < p.cols && blockIdx.z * p.cols + c < p.dv)
+                             ? fr_load(vals + (size_t)(t0 + t) * p.ld_v + c) : 0.f;
         }
     };
     auto put = [&](int b) {
-        float* dst = gsm + (size_t)b * buf_floats;
+        float* dst = gsm + (size_t)b * BUF;
 #pragma unroll
         for (int it = 0; it < N_IT; ++it) {
-            const int idx = tid + it * threads;
+            const int idx = tid + it * 128;
             if (idx < GEN_TOKENS * VEC) dst[idx] = held[it];
         }
-        for (int it = 0; it < n_v && it < 2; ++it) {
-            const int idx = tid + it * threads;
-            if (idx < GEN_TOKENS * p.cols) dst[GEN_TOKENS * VEC + idx] = held_v[it];
+#pragma unroll
+        for (int it = 0; it < N_V; ++it) {
+            const int idx = tid + it * 128;
+            if (idx < GEN_TOKENS * COLS) dst[GEN_TOKENS * VEC + idx] = held_v[it];
         }
     };
     const int chunks = (n + GEN_TOKENS - 1) / GEN_TOKENS;
+    float* out_at = p.out + (size_t)r0 * ((size_t)p.heads * p.dv) + head * p.dv + col;
     fetch(0);
     put(0);
     __syncthreads();
     for (int c = 0; c < chunks; ++c) {
         const int t0 = c * GEN_TOKENS, nt = min(GEN_TOKENS, n - t0);
         if (c + 1 < chunks) fetch(t0 + GEN_TOKENS);
-        const float* buf = gsm + (size_t)(c & 1) * buf_floats;
+        const float* buf = gsm + (size_t)(c & 1) * BUF;
         for (int t = 0; t < nt; ++t) {
             const float4* w4 = (const float4*)(buf + t * VEC) + part;
             const float4* b4 = w4 + DKP / 4;
@@ -610,20 +615,20 @@ __global__ void __launch_bounds__(128) general_scan_kernel(GeneralScanArgs p) {
             float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll
             for (int m = 0; m < PER / 4; ++m) {
-                const float4 u = u4[4 * m];
+                const float4 u = u4[LPC * m];
                 d0 = fmaf(u.x, s[4 * m], d0);
                 d1 = fmaf(u.y, s[4 * m + 1], d1);
                 d2 = fmaf(u.z, s[4 * m + 2], d2);
                 d3 = fmaf(u.w, s[4 * m + 3], d3);
             }
             float dot = (d0 + d1) + (d2 + d3);
-            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-            dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-            const float val = buf[GEN_TOKENS * VEC + t * p.cols + (local_col < p.cols ? local_col : 0)];
+#pragma unroll
+            for (int o = 1; o < LPC; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+            const float val = buf[GEN_TOKENS * VEC + t * COLS + local_col];
             float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
             for (int m = 0; m < PER / 4; ++m) {
-                const float4 w = w4[4 * m], b = b4[4 * m], k = k4[4 * m], r = r4[4 * m];
+                const float4 w = w4[LPC * m], b = b4[LPC * m], k = k4[LPC * m], r = r4[LPC * m];
                 s[4 * m] = fmaf(k.x, val, fmaf(-b.x, dot, w.x * s[4 * m]));
                 s[4 * m + 1] = fmaf(k.y, val, fmaf(-b.y, dot, w.y * s[4 * m + 1]));
                 s[4 * m + 2] = fmaf(k.z, val, fmaf(-b.z, dot, w.z * s[4 * m + 2]));
@@ -634,9 +639,9 @@ __global__ void __launch_bounds__(128) general_scan_kernel(GeneralScanArgs p) {
                 o3 = fmaf(r.w, s[4 * m + 3], o3);
             }
             float o = (o0 + o1) + (o2 + o3);
-            o += __shfl_xor_sync(0xffffffffu, o, 1);
-            o += __shfl_xor_sync(0xffffffffu, o, 2);
-            if (part == 0 && live_col) p.out[(size_t)(r0 + t0 + t) * ((size_t)p.heads * p.dv) + head * p.dv + col] = o;
+#pragma unroll
+            for (int x = 1; x < LPC; x <<= 1) o += __shfl_xor_sync(0xffffffffu, o, x);
+            if (part == 0 && live_col) out_at[(size_t)(t0 + t) * p.heads * p.dv] = o;
         }
         if (c + 1 < chunks) put((c + 1) & 1);
         __syncthreads();
@@ -644,30 +649,42 @@ __global__ void __launch_bounds__(128) general_scan_kernel(GeneralScanArgs p) {
     if (live_col) {
 #pragma unroll
         for (int j = 0; j < PER; ++j) {
-            const int i = 4 * (4 * (j >> 2) + part) + (j & 3);
+            const int i = 4 * (LPC * (j >> 2) + part) + (j & 3);
             if (i < p.dk) S[(size_t)i * p.dv + col] = s[j];
         }
     }
 }
 
-template <typename T, int DKP>
-int launch_general(const GeneralScanArgs& p, int n_seqs, cudaStream_t stream) {
-    const size_t smem = (size_t)2 * gen_tokens(DKP) * (5 * DKP + p.cols) * sizeof(float);
-    if (smem > 48 * 1024) FR_CUDA(cudaFuncSetAttribute(general_scan_kernel<T, DKP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+template <typename T, int DKP, int LPC>
+int launch_general(GeneralScanArgs p, int n_seqs, cudaStream_t stream) {
+    constexpr int COLS = 128 / LPC;
+    p.cols = COLS;
+    if (p.cols > ((p.dv + 7) / 8) * 8) p.cols = ((p.dv + 7) / 8) * 8;      // few value channels: the rest of the block only helps to stage
+    const size_t smem = (size_t)2 * gen_tokens(DKP, LPC) * (5 * DKP + COLS) * sizeof(float);
+    if (smem > 48 * 1024) FR_CUDA(cudaFuncSetAttribute(general_scan_kernel<T, DKP, LPC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const dim3 grid(n_seqs, p.heads, (p.dv + p.cols - 1) / p.cols);
-    // always 128 threads: those beyond the block's columns only help to stage
-    FR_CUDA(fr_launch(general_scan_kernel<T, DKP>, grid, dim3(128), smem, stream, p));
+    FR_CUDA(fr_launch(general_scan_kernel<T, DKP, LPC>, grid, dim3(128), smem, stream, p));
     FR_CHECK_LAUNCH("general delta scan");
     return FR_OK;
 }
 
+template <typename T, int DKP>
+int general_by_lanes(const GeneralScanArgs& p, int n_seqs, cudaStream_t stream) {
+    if constexpr (DKP >= 64) {
+        // sixteen lanes per column while four would leave schedulers without a warp (four per SM)
+        const int sms = fr_sm_count() > 0 ? fr_sm_count() : 128;
+        if ((long long)n_seqs * p.heads * p.dv * 4 / 32 < 8LL * sms) return launch_general<T, DKP, 16>(p, n_seqs, stream);
+    }
+    return launch_general<T, DKP, 4>(p, n_seqs, stream);
+}
+
 template <typename T>
 int general_by_size(const GeneralScanArgs& p, int n_seqs, cudaStream_t stream) {
-    if (p.dk <= 16) return launch_general<T, 16>(p, n_seqs, stream);
-    if (p.dk <= 32) return launch_general<T, 32>(p, n_seqs, stream);
-    if (p.dk <= 64) return launch_general<T, 64>(p, n_seqs, stream);
-    if (p.dk <= 128) return launch_general<T, 128>(p, n_seqs, stream);
-    if (p.dk <= 256) return launch_general<T, 256>(p, n_seqs, stream);
+    if (p.dk <= 16) return general_by_lanes<T, 16>(p, n_seqs, stream);
+    if (p.dk <= 32) return general_by_lanes<T, 32>(p, n_seqs, stream);
+    if (p.dk <= 64) return general_by_lanes<T, 64>(p, n_seqs, stream);
+    if (p.dk <= 128) return general_by_lanes<T, 128>(p, n_seqs, stream);
+    if (p.dk <= 256) return general_by_lanes<T, 256>(p, n_seqs, stream);
     FR_REFUSE("general delta scan: %d key channels per head (at most 256)", p.dk);
 }
 
@@ -700,11 +717,7 @@ FR_EXPORT int delta_general_scan(const float* prep, const void* v, int ld_v, int
     GeneralScanArgs p;
     p.prep = prep; p.v = v; p.out = out; p.state = state; p.state_stride = state_stride; p.s_off = s_off; p.seq_start = seq_start;
     p.seq_qlen = seq_qlen; p.seq_slots = seq_slots; p.ld_v = ld_v; p.v_off = v_off; p.heads = heads; p.dk = dk; p.dv = dv;
-    const int sms = fr_sm_count() > 0 ? fr_sm_count() : 128;
-    int cols = 32;
-    if ((long long)n_seqs * heads * ((dv + cols - 1) / cols) < 2LL * sms) cols = 16;
-    if (cols > ((dv + 7) / 8) * 8) cols = ((dv + 7) / 8) * 8;
-    p.cols = cols;
+    p.cols = 0;                                      // chosen with the lanes per column
     if (dtype == FR_F32) return general_by_size<float>(p, n_seqs, stream);
     if (dtype == FR_BF16) return general_by_size<bf16>(p, n_seqs, stream);
     FR_REFUSE("general delta scan: unknown dtype %d", dtype);

@@ -829,86 +829,121 @@ struct NormConvArgs {
     const int* seq_qlen;
     const int* seq_slots;
     int width, n, shift;     // shift: every sequence brings one row and the history moves on in the same kernel
+    int rows, tile, cols;    // rows of the step; rows per block; columns per block
     float eps;
 };
 
-// mean and 1 / sqrt(variance + eps) of one row
-__device__ __forceinline__ void row_stats(const float* xr, int width, float eps, float* partial, float& mean, float& inv) {
-    float sum = 0.f;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) sum += xr[i];
-    mean = block_sum(sum, partial) / (float)width;
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        const float d = xr[i] - mean;
-        ss = fmaf(d, d, ss);
+constexpr int CONV_MAX_TAPS = 8, CONV_TILE = 4;
+
+// mean and 1 / sqrt(variance + eps) of one row, by one warp (two passes: the variance is the mean of the squared deviations)
+__device__ __forceinline__ void warp_row_stats(const float* xr, int width, float eps, int lane, float& mean, float& inv) {
+    float sum = 0.f, ss = 0.f;
+    if ((width & 3) == 0 && (((uintptr_t)xr) & 15) == 0) {
+        const float4* x4 = (const float4*)xr;
+#pragma unroll 8
+        for (int i = lane; i < width / 4; i += 32) {
+            const float4 v = x4[i];
+            sum += (v.x + v.y) + (v.z + v.w);
+        }
+        mean = fr_warp_sum(sum) / (float)width;
+#pragma unroll 8
+        for (int i = lane; i < width / 4; i += 32) {
+            const float4 v = x4[i];
+            const float a = v.x - mean, b = v.y - mean, c = v.z - mean, d = v.w - mean;
+            ss += (a * a + b * b) + (c * c + d * d);
+        }
+    } else {
+        for (int i = lane; i < width; i += 32) sum += xr[i];
+        mean = fr_warp_sum(sum) / (float)width;
+        for (int i = lane; i < width; i += 32) {
+            const float d = xr[i] - mean;
+            ss = fmaf(d, d, ss);
+        }
     }
-    inv = 1.0f / sqrtf(block_sum(ss, partial) / (float)width + eps);
+    inv = 1.0f / sqrtf(fr_warp_sum(ss) / (float)width + eps);
 }
 
-constexpr int CONV_MAX_TAPS = 8;
-
+// A block owns `tile` consecutive rows of the step and `cols` columns.  Its warps first take the statistics of those rows and
+// of the n - 1 rows before them (once per row, not once per tap), then every thread walks its columns: the normed rows that
+// the taps reach are formed again from x (they are in L1 by then) or, before a step's first row, read from the history.
 template <typename TO>
 __global__ void __launch_bounds__(256) norm_conv_kernel(NormConvArgs p) {
-    __shared__ float partial[32];
-    __shared__ float stats[CONV_MAX_TAPS][2];
+    __shared__ float stats[CONV_TILE + CONV_MAX_TAPS][2];
     fr_pdl_wait();
     fr_pdl_launch();
-    const int row = blockIdx.x, seq = p.row_seq[row];
-    TO* yr = (TO*)p.y + (size_t)row * p.width;
-    if (seq < 0) {
-        for (int i = threadIdx.x; i < p.width; i += blockDim.x) fr_store(yr + i, 0.f);
-        return;
-    }
-    const int t = row - p.seq_start[seq];               // rows of this sequence before this one in the step
-    float* hist = p.state + (size_t)p.seq_slots[seq] * p.stride + p.offset;
-    // statistics of the rows of the step that the taps reach: d rows back, d = 0 .. n - 1
-    for (int d = 0; d < p.n && d <= t; ++d) {
+    const int r0 = blockIdx.x * p.tile, r1 = min(r0 + p.tile, p.rows);
+    const int first = p.shift ? r0 : max(0, r0 - (p.n - 1));          // one row per sequence: no row of the step is another's neighbour
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int r = first + warp; r < r1; r += 8) {
         float mean, inv;
-        row_stats(p.x + (size_t)(row - d) * p.width, p.width, p.eps, partial, mean, inv);
-        if (threadIdx.x == 0) {
-            stats[d][0] = mean;
-            stats[d][1] = inv;
+        warp_row_stats(p.x + (size_t)r * p.width, p.width, p.eps, lane, mean, inv);
+        if (lane == 0) {
+            stats[r - first][0] = mean;
+            stats[r - first][1] = inv;
         }
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < p.width; i += blockDim.x) {
-        const float wi = p.w.at(i), bi = p.b.p != nullptr ? p.b.at(i) : 0.f;
-        float acc = 0.f, own = 0.f, older[CONV_MAX_TAPS];
-        for (int d = p.n - 1; d >= 0; --d) {              // oldest first
-            float h;
-            if (d <= t) h = round_as<TO>((p.x[(size_t)(row - d) * p.width + i] - stats[d][0]) * stats[d][1] * wi + bi);
-            else h = hist[(size_t)(p.n - 1 - (d - t)) * p.width + i];       // d - t rows before the step's first
-            older[d] = h;
-            acc = fmaf(p.taps.at(i * p.n + (p.n - 1 - d)), h, acc);
-            if (d == 0) own = h;
+    const int c0 = blockIdx.y * p.cols, c1 = min(c0 + p.cols, p.width);
+    for (int row = r0; row < r1; ++row) {
+        const int seq = p.row_seq[row];
+        TO* yr = (TO*)p.y + (size_t)row * p.width;
+        if (seq < 0) {
+            for (int i = c0 + threadIdx.x; i < c1; i += blockDim.x) fr_store(yr + i, 0.f);
+            continue;
         }
-        fr_store(yr + i, own + acc);
-        if (p.shift)                                      // one row per sequence: the history takes it now
-            for (int k = 0; k + 1 < p.n; ++k) hist[(size_t)k * p.width + i] = older[p.n - 2 - k];
+        const int t = row - p.seq_start[seq];               // rows of this sequence before this one in the step
+        float* hist = p.state + (size_t)p.seq_slots[seq] * p.stride + p.offset;
+        for (int i = c0 + threadIdx.x; i < c1; i += blockDim.x) {
+            const float wi = p.w.at(i), bi = p.b.p != nullptr ? p.b.at(i) : 0.f;
+            float acc = 0.f, own = 0.f, older[CONV_MAX_TAPS];
+            for (int d = p.n - 1; d >= 0; --d) {              // oldest first
+                float h;
+                if (d <= t) h = round_as<TO>((p.x[(size_t)(row - d) * p.width + i] - stats[row - d - first][0]) * stats[row - d - first][1] * wi + bi);
+                else h = hist[(size_t)(p.n - 1 - (d - t)) * p.width + i];       // d - t rows before the step's first
+                older[d] = h;
+                acc = fmaf(p.taps.at(i * p.n + (p.n - 1 - d)), h, acc);
+                if (d == 0) own = h;
+            }
+            fr_store(yr + i, own + acc);
+            if (p.shift)                                      // one row per sequence: the history takes it now
+                for (int k = 0; k + 1 < p.n; ++k) hist[(size_t)k * p.width + i] = older[p.n - 2 - k];
+        }
     }
 }
 
 // After norm_conv: the history of every sequence takes the step's last n - 1 rows h (a step of fewer rows keeps the
-// youngest of what it had).  One block per sequence; a thread owns its channels, reads before it writes, and moves old rows
-// towards the front in rising order, so nothing is read after it was overwritten.
+// youngest of what it had).  A block per sequence and entry where the step brings n - 1 rows or more (every entry is a row of
+// the step then); for shorter steps one block per sequence walks the entries in rising order, a thread owning its columns, so
+// that nothing is read after it was overwritten.
 template <typename TO>
 __global__ void __launch_bounds__(256) norm_conv_state_kernel(NormConvArgs p) {
-    __shared__ float partial[32];
     fr_pdl_wait();
     fr_pdl_launch();
     const int seq = blockIdx.x, qlen = p.seq_qlen[seq], first = p.seq_start[seq];
     if (qlen <= 0) return;
     float* hist = p.state + (size_t)p.seq_slots[seq] * p.stride + p.offset;
-    for (int k = 0; k + 1 < p.n; ++k) {
+    const bool alone = qlen < p.n - 1;                        // entries move: this block does them all, in order
+    if (alone && blockIdx.y != 0) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __shared__ float st[2];
+    for (int k = alone ? 0 : blockIdx.y; k < (alone ? p.n - 1 : (int)blockIdx.y + 1); ++k) {
         const int s = qlen - (p.n - 1) + k;               // row of the step that becomes entry k; negative: an old entry
         if (s < 0) {
             for (int i = threadIdx.x; i < p.width; i += blockDim.x) hist[(size_t)k * p.width + i] = hist[(size_t)(k + qlen) * p.width + i];
         } else {
-            float mean, inv;
             const float* xr = p.x + (size_t)(first + s) * p.width;
-            row_stats(xr, p.width, p.eps, partial, mean, inv);
+            __syncthreads();
+            if (warp == 0) {
+                float mean, inv;
+                warp_row_stats(xr, p.width, p.eps, lane, mean, inv);
+                if (lane == 0) {
+                    st[0] = mean;
+                    st[1] = inv;
+                }
+            }
+            __syncthreads();
             for (int i = threadIdx.x; i < p.width; i += blockDim.x)
-                hist[(size_t)k * p.width + i] = round_as<TO>((xr[i] - mean) * inv * p.w.at(i) + (p.b.p != nullptr ? p.b.at(i) : 0.f));
+                hist[(size_t)k * p.width + i] = round_as<TO>((xr[i] - st[0]) * st[1] * p.w.at(i) + (p.b.p != nullptr ? p.b.at(i) : 0.f));
         }
     }
 }
@@ -962,9 +997,15 @@ FR_EXPORT int residual_norm_conv(const float* x, const void* w, const void* b, i
     NormConvArgs p;
     p.x = x; p.w = FrVec{w, w_dtype}; p.b = FrVec{b, w_dtype}; p.taps = FrVec{taps, taps_dtype}; p.y = y; p.state = state; p.stride = stride;
     p.offset = offset; p.row_seq = row_seq; p.seq_start = seq_start; p.seq_qlen = nullptr; p.seq_slots = seq_slots; p.width = width; p.n = n;
-    p.shift = shift && n > 1 ? 1 : 0; p.eps = eps;
-    if (out_dtype == FR_F32) FR_CUDA(fr_launch(norm_conv_kernel<float>, dim3(n_rows), dim3(256), 0, stream, p));
-    else if (out_dtype == FR_BF16) FR_CUDA(fr_launch(norm_conv_kernel<bf16>, dim3(n_rows), dim3(256), 0, stream, p));
+    p.shift = shift ? 1 : 0; p.eps = eps; p.rows = n_rows;
+    // many rows: tiles of rows with all columns; few rows: a row per block and the columns spread over eight blocks
+    p.tile = n_rows >= 512 ? CONV_TILE : 1;
+    int splits = n_rows >= 512 ? 1 : (n_rows >= 64 ? 2 : 8);
+    if (width < 256 * splits) splits = (width + 255) / 256;
+    p.cols = ((width + splits - 1) / splits + 3) / 4 * 4;
+    const dim3 grid((n_rows + p.tile - 1) / p.tile, (width + p.cols - 1) / p.cols);
+    if (out_dtype == FR_F32) FR_CUDA(fr_launch(norm_conv_kernel<float>, grid, dim3(256), 0, stream, p));
+    else if (out_dtype == FR_BF16) FR_CUDA(fr_launch(norm_conv_kernel<bf16>, grid, dim3(256), 0, stream, p));
     else FR_REFUSE("norm_conv: unknown dtype %d", out_dtype);
     FR_CHECK_LAUNCH("norm_conv");
     return FR_OK;
@@ -978,9 +1019,10 @@ FR_EXPORT int residual_norm_conv_state(const float* x, const void* w, const void
     NormConvArgs p;
     p.x = x; p.w = FrVec{w, w_dtype}; p.b = FrVec{b, w_dtype}; p.taps = FrVec{nullptr, 0}; p.y = nullptr; p.state = state; p.stride = stride;
     p.offset = offset; p.row_seq = nullptr; p.seq_start = seq_start; p.seq_qlen = seq_qlen; p.seq_slots = seq_slots; p.width = width; p.n = n;
-    p.shift = 0; p.eps = eps;
-    if (out_dtype == FR_F32) FR_CUDA(fr_launch(norm_conv_state_kernel<float>, dim3(n_seqs), dim3(256), 0, stream, p));
-    else if (out_dtype == FR_BF16) FR_CUDA(fr_launch(norm_conv_state_kernel<bf16>, dim3(n_seqs), dim3(256), 0, stream, p));
+    p.shift = 0; p.eps = eps; p.rows = 0; p.tile = 1; p.cols = width;
+    const dim3 grid(n_seqs, n - 1);
+    if (out_dtype == FR_F32) FR_CUDA(fr_launch(norm_conv_state_kernel<float>, grid, dim3(256), 0, stream, p));
+    else if (out_dtype == FR_BF16) FR_CUDA(fr_launch(norm_conv_state_kernel<bf16>, grid, dim3(256), 0, stream, p));
     else FR_REFUSE("norm_conv: unknown dtype %d", out_dtype);
     FR_CHECK_LAUNCH("norm_conv_state");
     return FR_OK;

@@ -496,7 +496,7 @@ Tensor Ops::general_delta(const Tensor& proj, const Tensor& z, const Tensor& a_r
     const auto& k = kernels::delta();
     float* prep = scratch_floats(proj.rows() * hk * 5);
     Tensor o = alloc(DType::F32, proj.rows(), hv);
-    Timed t(*this, Other);
+    Timed t(*this, Attention);                       // counted with the attention kernels and the other scans
     call(launches_, k, k.general_prepare(proj.data, (int)proj.ld, (int)s.r_off, (int)s.k_off, (const float*)z.data, (int)z.ld, (const float*)a_raw.data,
                                          (int)a_raw.ld, z_bias.data, a_bias.data, code(z_bias.dtype), prep, (int)proj.rows(), s.heads, s.dk, s.rate,
                                          s.unit_eps, code(proj.dtype), stream_), "general_prepare");
