@@ -384,7 +384,8 @@ __global__ void __launch_bounds__(128, 3) prompt_kernel(PromptArgs p) {
     bf16* sq = (bf16*)smem_raw;                           // [BM][DK + PAD]
     bf16* sk = sq + BM * (DK + PAD);                      // [BN][DK + PAD]
     bf16* svt = sk + BN * (DK + PAD);                     // [DV][BN + PAD]
-    const int seq = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * BM;
+    // the last row tiles first: without a window they walk the most keys, and the short ones then fill the grid's tail
+    const int seq = blockIdx.z, h = blockIdx.y, q0 = (gridDim.x - 1 - blockIdx.x) * BM;
     const int qlen = p.seq_qlen[seq];
     if (q0 >= qlen) return;
     const int row0 = p.seq_start[seq] + q0, pos0 = p.seq_pos0[seq] + q0;

@@ -539,14 +539,18 @@ struct GeneralScanArgs {
 // tokens staged at a time: fewer where a token is wide, so that what a thread holds of the next chunk stays in registers
 constexpr int gen_tokens(int dkp, int lpc) { return lpc >= 16 ? (dkp <= 128 ? 8 : 4) : (dkp <= 64 ? 8 : (dkp <= 128 ? 4 : 2)); }
 
+// threads of a block.  (Blocks of 512 threads for the sixteen-lane form, which would share a token's staged vectors among
+// 32 columns instead of 8, ran 1.5 times slower: sixteen warps then queue at one SM's shared memory while other SMs idle.)
+constexpr int scan_threads(int) { return 128; }
+
 // DKP: key channels rounded up to 16, 32, 64, 128 or 256.  LPC lanes share a value channel (a column of S): 4, or 16 where
 // the step has few sequences (a lane's share of a token is then a quarter as long, and four times as many warps fill the
 // device); a lane holds DKP / LPC key channels, dealt out in groups of four so that the lanes of a column read neighbouring
 // 16-byte pieces of shared memory.
 template <typename T, int DKP, int LPC>
-__global__ void __launch_bounds__(128) general_scan_kernel(GeneralScanArgs p) {
+__global__ void __launch_bounds__(scan_threads(LPC)) general_scan_kernel(GeneralScanArgs p) {
     extern __shared__ __align__(16) float gsm[];
-    constexpr int PER = DKP / LPC, VEC = 5 * DKP, GEN_TOKENS = gen_tokens(DKP, LPC), COLS = 128 / LPC;
+    constexpr int PER = DKP / LPC, VEC = 5 * DKP, GEN_TOKENS = gen_tokens(DKP, LPC), THREADS = scan_threads(LPC), COLS = THREADS / LPC;
     static_assert(PER >= 4 && PER % 4 == 0, "a lane holds whole groups of four key channels");
     const int seq = blockIdx.x, head = blockIdx.y, tid = threadIdx.x;
     const int part = tid % LPC, local_col = tid / LPC, col = blockIdx.z * p.cols + local_col;
@@ -564,7 +568,7 @@ __global__ void __launch_bounds__(128) general_scan_kernel(GeneralScanArgs p) {
     }
     constexpr int BUF = GEN_TOKENS * (VEC + COLS);
     // what one thread loads of a chunk: vectors (w, a u, u, k, r padded to DKP with zeros) and the block's value channels
-    constexpr int N_IT = (GEN_TOKENS * VEC + 127) / 128, N_V = (GEN_TOKENS * COLS + 127) / 128;
+    constexpr int N_IT = (GEN_TOKENS * VEC + THREADS - 1) / THREADS, N_V = (GEN_TOKENS * COLS + THREADS - 1) / THREADS;
     float held[N_IT], held_v[N_V];
     const float* prep = p.prep + ((size_t)r0 * p.heads + head) * 5 * p.dk;
     const T* vals = (const T*)p.v + (size_t)r0 * p.ld_v + p.v_off + head * p.dv + blockIdx.z * p.cols;
@@ -572,13 +576,13 @@ __global__ void __launch_bounds__(128) general_scan_kernel(GeneralScanArgs p) {
         const int nt = min(GEN_TOKENS, n - t0);
 #pragma unroll
         for (int it = 0; it < N_IT; ++it) {
-            const int idx = tid + it * 128;
+            const int idx = tid + it * THREADS;
             const int t = idx / VEC, rest = idx - t * VEC, which = rest / DKP, i = rest - which * DKP;
             held[it] = (idx < GEN_TOKENS * VEC && t < nt && i < p.dk) ? prep[(size_t)(t0 + t) * p.heads * 5 * p.dk + which * p.dk + i] : 0.f;
         }
 #pragma unroll
         for (int it = 0; it < N_V; ++it) {
-            const int idx = tid + it * 128;
+            const int idx = tid + it * THREADS;
             const int t = idx / COLS, c = idx - t * COLS;
             held_v[it] = (idx < GEN_TOKENS * COLS && t < nt && c < p.cols && blockIdx.z * p.cols + c < p.dv)
                              ? fr_load(vals + (size_t)(t0 + t) * p.ld_v + c) : 0.f;
@@ -588,12 +592,12 @@ __global__ void __launch_bounds__(128) general_scan_kernel(GeneralScanArgs p) {
         float* dst = gsm + (size_t)b * BUF;
 #pragma unroll
         for (int it = 0; it < N_IT; ++it) {
-            const int idx = tid + it * 128;
+            const int idx = tid + it * THREADS;
             if (idx < GEN_TOKENS * VEC) dst[idx] = held[it];
         }
 #pragma unroll
         for (int it = 0; it < N_V; ++it) {
-            const int idx = tid + it * 128;
+            const int idx = tid + it * THREADS;
             if (idx < GEN_TOKENS * COLS) dst[GEN_TOKENS * VEC + idx] = held_v[it];
         }
     };
@@ -606,7 +610,8 @@ __global__ void __launch_bounds__(128) general_scan_kernel(GeneralScanArgs p) {
         const int t0 = c * GEN_TOKENS, nt = min(GEN_TOKENS, n - t0);
         if (c + 1 < chunks) fetch(t0 + GEN_TOKENS);
         const float* buf = gsm + (size_t)(c & 1) * BUF;
-        for (int t = 0; t < nt; ++t) {
+        // one token: the state decays, loses its part along the unit key, takes the new pair; returns this lane's share of the read-out
+        auto token = [&](int t) {
             const float4* w4 = (const float4*)(buf + t * VEC) + part;
             const float4* b4 = w4 + DKP / 4;
             const float4* u4 = b4 + DKP / 4;
@@ -638,10 +643,29 @@ __global__ void __launch_bounds__(128) general_scan_kernel(GeneralScanArgs p) {
                 o2 = fmaf(r.z, s[4 * m + 2], o2);
                 o3 = fmaf(r.w, s[4 * m + 3], o3);
             }
-            float o = (o0 + o1) + (o2 + o3);
+            return (o0 + o1) + (o2 + o3);
+        };
+        auto finish = [&](int t, float o) {
 #pragma unroll
             for (int x = 1; x < LPC; x <<= 1) o += __shfl_xor_sync(0xffffffffu, o, x);
             if (part == 0 && live_col) out_at[(size_t)(t0 + t) * p.heads * p.dv] = o;
+        };
+        if constexpr (LPC < 16) {
+            // the chunk's tokens unrolled, their read-outs summed over the lanes at the end of the chunk, so that a read-out
+            // overlaps the next token's chain (measured: 2.34 -> 1.99 ms for 8 x 1,024 tokens; with sixteen lanes it lost)
+            float res[GEN_TOKENS];
+#pragma unroll
+            for (int t = 0; t < GEN_TOKENS; ++t) {
+                if (t >= nt) break;
+                res[t] = token(t);
+            }
+#pragma unroll
+            for (int t = 0; t < GEN_TOKENS; ++t) {
+                if (t >= nt) break;
+                finish(t, res[t]);
+            }
+        } else {
+            for (int t = 0; t < nt; ++t) finish(t, token(t));
         }
         if (c + 1 < chunks) put((c + 1) & 1);
         __syncthreads();
@@ -657,13 +681,13 @@ __global__ void __launch_bounds__(128) general_scan_kernel(GeneralScanArgs p) {
 
 template <typename T, int DKP, int LPC>
 int launch_general(GeneralScanArgs p, int n_seqs, cudaStream_t stream) {
-    constexpr int COLS = 128 / LPC;
+    constexpr int COLS = scan_threads(LPC) / LPC;
     p.cols = COLS;
     if (p.cols > ((p.dv + 7) / 8) * 8) p.cols = ((p.dv + 7) / 8) * 8;      // few value channels: the rest of the block only helps to stage
     const size_t smem = (size_t)2 * gen_tokens(DKP, LPC) * (5 * DKP + COLS) * sizeof(float);
     if (smem > 48 * 1024) FR_CUDA(cudaFuncSetAttribute(general_scan_kernel<T, DKP, LPC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const dim3 grid(n_seqs, p.heads, (p.dv + p.cols - 1) / p.cols);
-    FR_CUDA(fr_launch(general_scan_kernel<T, DKP, LPC>, grid, dim3(128), smem, stream, p));
+    FR_CUDA(fr_launch(general_scan_kernel<T, DKP, LPC>, grid, dim3(scan_threads(LPC)), smem, stream, p));
     FR_CHECK_LAUNCH("general delta scan");
     return FR_OK;
 }
