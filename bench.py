@@ -657,7 +657,7 @@ def vulanex_config(width, layers=7, vocab=32768, window=1024, pool=64):
     of `window` tokens with pooled blocks of `pool` beside the generalized delta rule with heads of 128 x 128; input
     convolutions of four taps; a gated feed-forward of three times the width everywhere."""
     heads, kv = max(1, width // 128), max(1, width // 512)
-    att = {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "q_temp": {"coef": 0.5, "every": 64}}
+    att = {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "q_temp": {"coef": 0.3, "every": 128}}
     left = {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": window, "pool": pool},
             "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
     par = {"left": left, "right": {"heads": heads, "dim": 128, "decay_rank": 64}}

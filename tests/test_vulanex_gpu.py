@@ -59,9 +59,9 @@ CONFIGS = {
     "Q": (config(64, 200, [parallel(1, 1, 32, 8, 1, 1, 16, 1, 8, 500.0), attention(1, 1, 24, coef=1.0, every=1), parallel(1, 1, 8, 40, 7, 3, 2, 1, 40)],
                  [16, None, 32], taps=2, buckets=1, muls=(1, 0)), {0: 3, 2: 2}),
     # sizes that the tensor-core kernels like; prompts of several pages; a window of two pages and a block of a quarter page
-    "R": (config(128, 512, [parallel(4, 2, 32, 64, 128, 16, 32, 4, 32, 20000.0, (4.0, 256, 32.0, 1.0), 0.11), attention(4, 1, 64, 0.1, 0.5, 64),
+    "R": (config(128, 512, [parallel(4, 2, 32, 64, 128, 16, 32, 4, 32, 20000.0, (4.0, 256, 32.0, 1.0), 0.11), attention(4, 2, 64, 0.1, 0.4, 48),
                             parallel(4, 4, 64, 32, 96, 32, 16, 2, 64), attention(2, 2, 32)],
-                 [128, 64, 128, None], taps=3, buckets=509, muls=(127, 7), logit_scale=2.0), {0: 16, 2: 8}),
+                 [128, 64, 128, None], taps=3, buckets=251, muls=(61, 9), logit_scale=1.25), {0: 16, 2: 8}),
     # sizes that fit no tile: a width that is no multiple of 8, odd head sizes and counts, a block larger than the window,
     # a block larger than a page, one tap (no convolution history), eight taps elsewhere
     "S": (config(100, 333, [parallel(6, 2, 24, 40, 10, 30, 6, 3, 20, 777.0, (2.0, 100, 8.0, 0.5)), attention(5, 5, 10, coef=0.1, every=3),
