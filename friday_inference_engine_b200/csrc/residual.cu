@@ -835,10 +835,32 @@ struct NormConvArgs {
 
 constexpr int CONV_MAX_TAPS = 8, CONV_TILE = 4;
 
-// mean and 1 / sqrt(variance + eps) of one row, by one warp (two passes: the variance is the mean of the squared deviations)
+// mean and 1 / sqrt(variance + eps) of one row, by one warp (the variance is the mean of the squared deviations).  Rows of up
+// to 2,048 numbers in whole 16-byte pieces are read once, every load issued before any is used, and kept in registers for the
+// second sum; others are read twice.
 __device__ __forceinline__ void warp_row_stats(const float* xr, int width, float eps, int lane, float& mean, float& inv) {
+    constexpr int KEEP = 16;
     float sum = 0.f, ss = 0.f;
-    if ((width & 3) == 0 && (((uintptr_t)xr) & 15) == 0) {
+    const bool pieces = (width & 3) == 0 && (((uintptr_t)xr) & 15) == 0;
+    if (pieces && width <= KEEP * 128) {
+        const float4* x4 = (const float4*)xr;
+        float4 v[KEEP];
+#pragma unroll
+        for (int j = 0; j < KEEP; ++j) {
+            const int i = lane + 32 * j;
+            v[j] = i < width / 4 ? x4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < KEEP; ++j) sum += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+        mean = fr_warp_sum(sum) / (float)width;
+#pragma unroll
+        for (int j = 0; j < KEEP; ++j) {
+            if (lane + 32 * j < width / 4) {
+                const float a = v[j].x - mean, b = v[j].y - mean, c = v[j].z - mean, d = v[j].w - mean;
+                ss += (a * a + b * b) + (c * c + d * d);
+            }
+        }
+    } else if (pieces) {
         const float4* x4 = (const float4*)xr;
 #pragma unroll 8
         for (int i = lane; i < width / 4; i += 32) {
@@ -884,29 +906,51 @@ __global__ void __launch_bounds__(256) norm_conv_kernel(NormConvArgs p) {
     }
     __syncthreads();
     const int c0 = blockIdx.y * p.cols, c1 = min(c0 + p.cols, p.width);
-    for (int row = r0; row < r1; ++row) {
-        const int seq = p.row_seq[row];
-        TO* yr = (TO*)p.y + (size_t)row * p.width;
-        if (seq < 0) {
-            for (int i = c0 + threadIdx.x; i < c1; i += blockDim.x) fr_store(yr + i, 0.f);
-            continue;
+    // Columns outermost: a thread keeps, for its column, the taps and the normed values of the last rows in registers (hw[d]: d
+    // rows back), so that every row of x is normed once and the weights are read once per tile.  Loops over taps run to the
+    // compile-time maximum with the real number as a predicate, which keeps the windows in registers.
+    for (int i = c0 + threadIdx.x; i < c1; i += blockDim.x) {
+        const float wi = p.w.at(i), bi = p.b.p != nullptr ? p.b.at(i) : 0.f;
+        float tw[CONV_MAX_TAPS], hw[CONV_MAX_TAPS];
+#pragma unroll
+        for (int d = 0; d < CONV_MAX_TAPS; ++d) {
+            tw[d] = d < p.n ? p.taps.at(i * p.n + (p.n - 1 - d)) : 0.f;      // the tap that meets the row d back
+            hw[d] = 0.f;
         }
-        const int t = row - p.seq_start[seq];               // rows of this sequence before this one in the step
-        float* hist = p.state + (size_t)p.seq_slots[seq] * p.stride + p.offset;
-        for (int i = c0 + threadIdx.x; i < c1; i += blockDim.x) {
-            const float wi = p.w.at(i), bi = p.b.p != nullptr ? p.b.at(i) : 0.f;
-            float acc = 0.f, own = 0.f, older[CONV_MAX_TAPS];
-            for (int d = p.n - 1; d >= 0; --d) {              // oldest first
-                float h;
-                if (d <= t) h = round_as<TO>((p.x[(size_t)(row - d) * p.width + i] - stats[row - d - first][0]) * stats[row - d - first][1] * wi + bi);
-                else h = hist[(size_t)(p.n - 1 - (d - t)) * p.width + i];       // d - t rows before the step's first
-                older[d] = h;
-                acc = fmaf(p.taps.at(i * p.n + (p.n - 1 - d)), h, acc);
-                if (d == 0) own = h;
+        for (int r = first; r < r0; ++r) {                    // the rows before the tile that its taps reach
+#pragma unroll
+            for (int d = CONV_MAX_TAPS - 1; d > 0; --d) hw[d] = hw[d - 1];
+            hw[0] = round_as<TO>((p.x[(size_t)r * p.width + i] - stats[r - first][0]) * stats[r - first][1] * wi + bi);
+        }
+        for (int row = r0; row < r1; ++row) {
+            const int seq = p.row_seq[row];
+            TO* yr = (TO*)p.y + (size_t)row * p.width;
+#pragma unroll
+            for (int d = CONV_MAX_TAPS - 1; d > 0; --d) hw[d] = hw[d - 1];
+            hw[0] = round_as<TO>((p.x[(size_t)row * p.width + i] - stats[row - first][0]) * stats[row - first][1] * wi + bi);
+            if (seq < 0) {
+                fr_store(yr + i, 0.f);
+                continue;
             }
-            fr_store(yr + i, own + acc);
-            if (p.shift)                                      // one row per sequence: the history takes it now
-                for (int k = 0; k + 1 < p.n; ++k) hist[(size_t)k * p.width + i] = older[p.n - 2 - k];
+            const int t = row - p.seq_start[seq];               // rows of this sequence before this one in the step
+            float* hist = p.state + (size_t)p.seq_slots[seq] * p.stride + p.offset;
+            float acc = 0.f, seen[CONV_MAX_TAPS];
+#pragma unroll
+            for (int d = 0; d < CONV_MAX_TAPS; ++d) {
+                if (d < p.n) {
+                    // d rows back: a row of the step, or, before the step's first row, the history (oldest first)
+                    seen[d] = d <= t ? hw[d] : hist[(size_t)(p.n - 1 - (d - t)) * p.width + i];
+                    acc = fmaf(tw[d], seen[d], acc);
+                } else {
+                    seen[d] = 0.f;
+                }
+            }
+            fr_store(yr + i, hw[0] + acc);
+            if (p.shift) {                                    // one row per sequence: the history takes it now
+#pragma unroll
+                for (int d = 0; d < CONV_MAX_TAPS - 1; ++d)
+                    if (d < p.n - 1) hist[(size_t)(p.n - 2 - d) * p.width + i] = seen[d];
+            }
         }
     }
 }
